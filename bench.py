@@ -25,14 +25,21 @@ tuple: 4 taps x D channels).
 ``cpu_baseline``  the NumPy restatement of the reference evaluator, timed on
               this host on a bounded sample of the same workload.
 
-Multi-GPU (torchrun, one rank per GPU): the value tensor is replicated by an
-NCCL broadcast into each GPU's own memory (timed separately) and the queries
-are sharded in blocks: rank r owns queries [r*Q, (r+1)*Q) of a global set of
-N*Q queries per camera -- per-GPU work is fixed ("weak" scaling) and there is
-no collective on the data path.
+Multi-GPU (torchrun, one rank per GPU): "strong" scaling of the same step.  The
+10000 queries per camera are cut into N blocks, rank r owns block r of every
+camera; ``value`` is the whole job's samples over the slowest rank's time with
+the value tensor already replicated in each GPU's own memory (one NCCL
+broadcast, timed apart as ``value_broadcast_ms``).  ``with_value_replication``
+times the step with the replication inside it, pipelined per camera on a
+communication stream: broadcast from rank 0, and all-gather of a value that
+starts out S-sharded, in float32 and bfloat16.  ``e2e`` at N > 1 is
+``distributed.ShardedMsda.step``: a rank uploads 1/N of value and its own
+query block from pinned host memory, the ranks all-gather value over NVLink.
 
 ``--impl reference`` times the reference's CPU implementation of the same path
-(its NumPy evaluator, restated under oracle/) with every host thread.
+(its own NumPy evaluator from the git-ignored oracle/_ref when present, else its
+restatement under oracle/) with every host thread, and the reference CLI's
+single-thread loop beside it.
 """
 
 from __future__ import annotations
@@ -54,10 +61,10 @@ if str(ROOT) not in sys.path:
 METRIC = "BEVFormer-base SCA MSDA Gsamples/s"
 UNIT = "Gsamples/s"
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of msda_rows_kernel on
-# the base_sca workload (full size, one launch captured), from the ncu capture
-# summarised in profiles/msda_rows_kernel_base_sca.md.
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of msda_rows_kernel on the base_sca workload: constants
+# taken from one ncu capture of a full-size launch, not measured by this run (ncu cannot run inside a timed bench).
 NCU_TRAFFIC_BYTES = {"float32": 467_982_336, "bfloat16": 463_020_032}
+NCU_TRAFFIC_SOURCE = "constant from an ncu capture (one full-size launch, 2026-11-25), not measured in this run"
 
 
 def measured_peaks() -> tuple[float, str]:
@@ -142,6 +149,33 @@ def measured_tensor_peak() -> tuple[float, str]:
         return float(json.loads(path.read_text())["bf16_tflops"]), "measured bf16 burst"
     except Exception:
         return 1590.0, "fallback bf16 burst"
+
+
+def measure_tf32_peak(device, n: int = 8192, reps: int = 10) -> float:
+    """TFLOP/s of the library's TF32 GEMM (torch.matmul on float32 operands with TF32 products allowed), n^3,
+    best of `reps` single launches timed with CUDA events: the denominator for the TF32 mode of DCNv2, measured the
+    way the bf16 figure in MEASURED_PEAKS.json was (burst)."""
+    import torch
+
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        a = torch.randn((n, n), device=device)
+        b = torch.randn((n, n), device=device)
+        c = torch.empty((n, n), device=device)
+        for _ in range(3):
+            torch.matmul(a, b, out=c)
+        best = float("inf")
+        for _ in range(reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch.matmul(a, b, out=c)
+            e1.record()
+            torch.cuda.synchronize(device)
+            best = min(best, e0.elapsed_time(e1))
+        return 2.0 * n ** 3 / (best * 1e-3) / 1e12
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
 
 
 def measure_gather_rate(device, buffer_mb: float, launches: int = 10, lane_bytes: int = 16) -> float:
@@ -230,7 +264,9 @@ def bench_dcn(device, keys=("dcn_c4", "dcn_c5"), modes=("f32x3", "tf32", "bf16")
     from general_ai_compiler_b200.distributed import dcn_pixel_block, dcn_rank_pieces, unit_block
 
     peak, peak_kind = measured_tensor_peak()
-    out = {"unit": "TFLOP/s", "peak": peak, "peak_source": peak_kind}
+    tf32_peak = measure_tf32_peak(device)
+    out = {"unit": "TFLOP/s", "peak": peak, "peak_source": peak_kind, "tf32_peak": tf32_peak,
+           "tf32_peak_source": "torch.matmul fp32 8192^3 with TF32 products, best of 10, measured in this run"}
     if world > 1:
         out["sharding"] = (f"equal runs of output pixels over {world} ranks, one launch per rank; row_block_split = "
                            "(camera, output-row block) pieces; camera_split = contiguous camera blocks; time = max over ranks")
@@ -286,6 +322,8 @@ def bench_dcn(device, keys=("dcn_c4", "dcn_c5"), modes=("f32x3", "tf32", "bf16")
                     ms = reduce_max(ms)
                 tf = wl.flops / (ms * 1e-3) / 1e12
                 out[f"{key}/{math}{suffix}"] = {"ms": ms, "tflops": tf, "frac_of_bf16_peak": tf / peak}
+                if math == "tf32":
+                    out[f"{key}/{math}{suffix}"]["frac_of_tf32_peak"] = tf / tf32_peak
             if world == 1:
                 # the convolution that produces the offsets and mask scores (27 channels, split into the two DCNv2
                 # operands), and the bottleneck chain conv_offset -> DCNv2 with sigmoid, BatchNorm and ReLU folded in
@@ -490,63 +528,146 @@ def host_threads() -> int:
     return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
 
 
-def cpu_reference_throughput(workload, seconds_budget: float, steps: int, warmup: int):
-    """Times the NumPy restatement of the reference evaluator on a bounded sample.
+def _reference_evaluator():
+    """(callable(value, loc, attn, shapes) -> out, kind, what): the reference's own NumPy evaluator when the
+    git-ignored copy under oracle/_ref exists (made by oracle/make_ref.py from a checkout), else its restatement."""
+    import oracle
 
-    Returns (samples_per_second, per_step_ms list, description, threads)."""
+    if oracle.reference_available():
+        ref = oracle.load_reference()
+
+        def run(value, loc, attn, shapes):
+            return ref.evaluate_op("MSDeformableAttention", [value, loc, attn], {"spatial_shapes": [list(s) for s in shapes]})[0]
+
+        return run, "reference", "the reference's own gac.core.ops.evaluate_op"
+    from oracle.msda_numpy import msda_forward
+
+    return msda_forward, "port", "NumPy restatement of the reference evaluator (oracle/_ref absent)"
+
+
+def _over_threads(fn, value, loc, attn, shapes, threads: int):
+    """`fn` on (batch entry, query block) pieces spread over host threads (NumPy's gather loops drop the GIL);
+    every output element is produced by the evaluator's own arithmetic, pieces never share one."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    n_batch, n_query = loc.shape[0], loc.shape[1]
+    per_batch = max(1, -(-threads // n_batch))
+    step = max(1, -(-n_query // per_batch))
+    jobs = [(b, q0, min(n_query, q0 + step)) for b in range(n_batch) for q0 in range(0, n_query, step)]
+    out = np.empty((n_batch, n_query, value.shape[2] * value.shape[3]), np.float32)
+
+    def run(job):
+        b, q0, q1 = job
+        out[b:b + 1, q0:q1] = fn(value[b:b + 1], np.ascontiguousarray(loc[b:b + 1, q0:q1]),
+                                 np.ascontiguousarray(attn[b:b + 1, q0:q1]), shapes)
+
+    with ThreadPoolExecutor(max_workers=max(1, threads)) as pool:
+        list(pool.map(run, jobs))
+    return out
+
+
+def _sample_of(workload, total_queries: int):
+    cams = max(1, min(workload.batch, total_queries // workload.queries))
+    q_per_cam = min(workload.queries, max(1, total_queries // cams))
+    return type(workload)(workload.name, cams, q_per_cam, workload.heads, workload.head_dim, workload.points,
+                          workload.spatial_shapes, workload.location_model, workload.sigma, workload.seed)
+
+
+def cpu_reference_throughput(workload, seconds_budget: float, steps: int, warmup: int, single_thread_seconds: float = 0.0):
+    """Times the reference's CPU implementation of the path on a bounded sample of the workload.
+
+    Main figure: the evaluator given every host thread (query blocks in parallel).  Beside it, when
+    ``single_thread_seconds`` > 0, the figure of the reference's own command line -- one process, one thread,
+    ``reference_run`` in a ``perf_counter`` loop (src/gac/tools/cli.py:764-771).
+
+    Returns a dict: rate (samples/s), times_ms, sample, cores, kind, and optionally single_thread."""
     from general_ai_compiler_b200.bevformer import make_workload_inputs
-    from oracle.msda_numpy import msda_forward_threaded
 
+    fn, kind, what = _reference_evaluator()
     threads = host_threads()
-    probe = workload.with_queries(256)
-    probe = type(probe)(probe.name, 1, 256, probe.heads, probe.head_dim, probe.points, probe.spatial_shapes,
-                        probe.location_model, probe.sigma, probe.seed)
+    probe = _sample_of(workload, 256)
     x = make_workload_inputs(probe)
     args = (x["value"], x["sampling_locations"], x["attention_weights"], probe.spatial_shapes)
-    msda_forward_threaded(*args, threads=threads)
+    _over_threads(fn, *args, threads=threads)
     t0 = time.perf_counter()
-    msda_forward_threaded(*args, threads=threads)
+    _over_threads(fn, *args, threads=threads)
     rate = probe.samples / (time.perf_counter() - t0)
     per_step = seconds_budget / max(1, steps + warmup)
     per_query = workload.heads * workload.levels * workload.points
     q = int(max(threads * 16, min(workload.queries * workload.batch, rate * per_step / per_query)))
-    cams = max(1, min(workload.batch, q // workload.queries))
-    q_per_cam = min(workload.queries, max(1, q // cams))
-    sample = type(workload)(workload.name, cams, q_per_cam, workload.heads, workload.head_dim, workload.points,
-                            workload.spatial_shapes, workload.location_model, workload.sigma, workload.seed)
+    sample = _sample_of(workload, q)
     x = make_workload_inputs(sample)
     args = (x["value"], x["sampling_locations"], x["attention_weights"], sample.spatial_shapes)
     for _ in range(warmup):
-        msda_forward_threaded(*args, threads=threads)
+        _over_threads(fn, *args, threads=threads)
     times = []
     for _ in range(steps):
         t0 = time.perf_counter()
-        msda_forward_threaded(*args, threads=threads)
+        _over_threads(fn, *args, threads=threads)
         times.append(time.perf_counter() - t0)
-    total = sum(times)
-    desc = (f"{cams} camera(s) x {q_per_cam} queries of {workload.name} per step "
-            f"({sample.samples} samples), NumPy evaluator restatement, {threads} host threads")
-    return sample.samples * steps / total, [t * 1e3 for t in times], desc, threads
+    res = {"rate": sample.samples * steps / sum(times), "times_ms": [t * 1e3 for t in times], "cores": threads, "kind": kind,
+           "sample": f"{sample.batch} camera(s) x {sample.queries} queries of {workload.name} per step "
+                     f"({sample.samples} samples), {what}, query blocks over {threads} host threads"}
+    if single_thread_seconds > 0:
+        res["single_thread"] = cpu_reference_cli_loop(workload, single_thread_seconds)
+    return res
+
+
+def cpu_reference_cli_loop(workload, seconds_budget: float) -> dict:
+    """One process, one thread: ``reference_run(graph, inputs)`` timed the way the reference's CLI times its
+    ``numpy-cpu`` backend (one warm-up, then ``perf_counter`` around each call; src/gac/tools/cli.py:764-771),
+    on a sample sized to the budget.  Falls back to the restated evaluator when oracle/_ref is absent."""
+    import oracle
+    from general_ai_compiler_b200.bevformer import make_workload_inputs
+
+    fn, kind, what = _reference_evaluator()
+    rate_guess = 0.6e6                                       # samples/s of the NumPy loop on one core, roughly
+    per_query = workload.heads * workload.levels * workload.points
+    sample = _sample_of(workload, int(max(64, min(workload.queries * workload.batch, rate_guess * seconds_budget / 3 / per_query))))
+    x = make_workload_inputs(sample)
+    if kind == "reference":
+        ref = oracle.load_reference()
+        graph = oracle.reference_msda_graph(ref, sample.batch, sample.spatial_size, sample.queries, sample.heads,
+                                            sample.head_dim, sample.levels, sample.points, sample.spatial_shapes)
+        call = lambda: ref.reference_run(graph, x)
+        what = "the reference's own reference_run (input validation + evaluate_node)"
+    else:
+        call = lambda: fn(x["value"], x["sampling_locations"], x["attention_weights"], sample.spatial_shapes)
+    call()
+    times = []
+    for _ in range(2):
+        t0 = time.perf_counter()
+        call()
+        times.append(time.perf_counter() - t0)
+    return {"value": sample.samples / (sum(times) / len(times)) / 1e9, "unit": UNIT, "cores": 1, "kind": kind,
+            "sample": f"{sample.batch} camera(s) x {sample.queries} queries ({sample.samples} samples), {what}"}
 
 
 def run_reference_arm(args, workload) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    rate, times, desc, threads = cpu_reference_throughput(workload, args.cpu_seconds, args.steps, args.warmup)
-    value = rate / 1e9
+    r = cpu_reference_throughput(workload, args.cpu_seconds, args.steps, args.warmup, single_thread_seconds=max(0.5, min(15.0, args.cpu_seconds / 8)))
+    value = r["rate"] / 1e9
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": float(np.mean(times)),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload.name, "cameras": workload.batch, "queries_per_camera": workload.queries,
-                   "levels": workload.levels, "points": workload.points, "heads": workload.heads,
-                   "head_dim": workload.head_dim, "note": "CPU arm: each step is a bounded sample of the workload"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc},
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": float(np.mean(r["times_ms"])),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": bench_config(workload, max(1, args.gpus)) | {"note": "CPU arm: each step is a bounded sample of the workload"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": r["cores"], "kind": r["kind"], "sample": r["sample"],
+                         "single_thread_cli_loop": r.get("single_thread")},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+def bench_config(workload, world: int) -> dict:
+    """The `config` object both arms print (same keys, so the two lines describe one configuration)."""
+    return {"workload": workload.name, "cameras": workload.batch, "global_queries_per_camera": workload.queries,
+            "levels": workload.levels, "points": workload.points, "heads": workload.heads, "head_dim": workload.head_dim,
+            "spatial_shapes": [list(s) for s in workload.spatial_shapes], "samples_per_step": workload.samples,
+            "sharding": f"{world} query block(s) of {workload.queries} queries per camera, value replicated"}
 
 
 def main() -> None:
@@ -602,7 +723,7 @@ def main() -> None:
 
     from general_ai_compiler_b200 import ops
     from general_ai_compiler_b200.compiler import compile_cuda
-    from general_ai_compiler_b200.distributed import broadcast_value, query_block
+    from general_ai_compiler_b200.distributed import ShardedMsda, bind_host_near_gpu, broadcast_value, query_block
     from general_ai_compiler_b200.session import CudaSession
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -629,14 +750,14 @@ def main() -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    # ---- inputs: the value slab is made on rank 0 and replicated; each rank draws its own query block
-    global_q = workload.queries * world
-    q0, q1 = query_block(global_q, world, rank)
-    assert q1 - q0 == workload.queries
-    local = workload
-    host = make_workload_inputs(local, seed=workload.seed + 7919 * rank)
-    if rank != 0:
-        host["value"] = np.empty_like(host["value"])
+    # ---- inputs: every rank draws the same seeded tensors and keeps its own query block of locations/weights;
+    # the value tensor is made on rank 0 and replicated into each GPU's own memory by one NCCL broadcast
+    numa_cpus = bind_host_near_gpu(local_rank) if world > 1 else None
+    q0, q1 = query_block(workload.queries, world, rank)
+    local = workload.with_queries(q1 - q0)
+    host = make_workload_inputs(workload)
+    host["sampling_locations"] = np.ascontiguousarray(host["sampling_locations"][:, q0:q1])
+    host["attention_weights"] = np.ascontiguousarray(host["attention_weights"][:, q0:q1])
     value_dev = torch.from_numpy(host["value"]).to(device) if rank == 0 else torch.empty(
         host["value"].shape, dtype=torch.float32, device=device)
     bcast_ms = 0.0
@@ -670,7 +791,7 @@ def main() -> None:
         total_ms, per_launch = timed_launches(value_dev, args.steps, args.warmup)
     total_ms = reduce_max(total_ms)
     clock_summary = clocks.summary()
-    total_samples = local.samples * world * args.steps
+    total_samples = workload.samples * args.steps            # the whole job: all ranks' query blocks together
     value_gs = total_samples / (total_ms * 1e-3) / 1e9
     avg_launch_ms = float(np.mean(per_launch))
 
@@ -682,7 +803,7 @@ def main() -> None:
     if rank == 0:
         from oracle import msda_c
 
-        nq = 64
+        nq = min(64, local.queries)
         want = msda_c(host["value"], host["sampling_locations"][:, :nq], host["attention_weights"][:, :nq],
                       local.spatial_shapes)
         got = out_dev[:, :nq].float().cpu().numpy()      # out_dev holds the bf16-value run: 1e-2 gate
@@ -707,31 +828,128 @@ def main() -> None:
             dist.destroy_process_group()
         return
 
-    # ---- end to end: CudaSession.run with pinned host buffers
+    # ---- N > 1: the step with the replication of `value` inside it.  The value starts out S-sharded (each rank
+    # holds 1/N of every camera's rows, as a value projection computed in parallel would leave it) or whole on rank
+    # 0; per camera it is all-gathered / broadcast over NVLink into each GPU's own memory on a communication stream
+    # while the kernel gathers from the previous camera's slab.
     e2e_steps = args.e2e_steps or min(args.steps, 20)
-    graph = build_msda_graph_for(local)
-    session = CudaSession(compile_cuda(graph), device_id=local_rank, check_finite=False, fresh_outputs=False,
-                          overlap_batches=True)
-    pinned = session.pinned_inputs()
-    if rank != 0:
-        host["value"] = value_dev.cpu().numpy()
-    for name, arr in host.items():
-        np.copyto(pinned[name], arr)
-    h2d = sum(int(a.nbytes) for a in pinned.values())
-    d2h = int(out_dev.numel() * 4)
-    for _ in range(3):
-        session.run(pinned)
-    barrier()
-    t0 = time.perf_counter()
-    gpu_ms = 0.0
-    for _ in range(e2e_steps):
-        res = session.run(pinned)
-        gpu_ms += res.gpu_stream_ms
-    barrier()
-    e2e_ms = reduce_max((time.perf_counter() - t0) * 1e3)
-    e2e_gs = local.samples * world * e2e_steps / (e2e_ms * 1e-3) / 1e9
-    e2e_out = res.outputs["output"]
-    session.close()
+    replication = None
+    sharded_e2e = None
+    if world > 1:
+        full_host = make_workload_inputs(workload)
+        replication = {"note": "device-resident step = per-camera collective on a communication stream + MSDA kernel on the "
+                               "compute stream, camera b+1 on the wire while camera b is gathered; ms = max over ranks",
+                       "kernel_only_ms_per_step": total_ms / args.steps}
+        rep_steps = max(5, min(args.steps, 50))
+
+        def timed_resident(runner, with_kernel: bool):
+            run = runner.step_resident if with_kernel else (lambda: [runner._replicate_entry(b) for b in range(runner.B)])
+            for _ in range(3):
+                run()
+            barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            done = torch.cuda.current_stream()
+            a.record(done)
+            runner.s_comm.wait_event(a)
+            runner.s_compute.wait_event(a)
+            for _ in range(rep_steps):
+                run()
+            done.wait_stream(runner.s_comm)
+            done.wait_stream(runner.s_compute)
+            b.record(done)
+            barrier()
+            return reduce_max(a.elapsed_time(b) / rep_steps)
+
+        for label, mode, storage in (("broadcast_f32", "broadcast", "float32"), ("all_gather_f32", "all_gather", "float32"),
+                                     ("all_gather_bf16", "all_gather", "bfloat16")):
+            runner = ShardedMsda(batch=workload.batch, spatial_shapes=workload.spatial_shapes, queries=workload.queries,
+                                 heads=workload.heads, head_dim=workload.head_dim, points=workload.points, device=device,
+                                 value_storage=storage, replicate=mode)
+            runner.load_host(full_host["value"], full_host["sampling_locations"], full_host["attention_weights"])
+            runner.upload()
+            if mode == "broadcast":
+                runner.set_broadcast_source(full_host["value"])
+            step_ms = timed_resident(runner, True)
+            coll_ms = timed_resident(runner, False)
+            item = 4 if storage == "float32" else 2
+            slab_bytes = workload.batch * workload.spatial_size * workload.heads * workload.head_dim * item
+            recv = slab_bytes * (world - 1) / world if mode == "all_gather" else slab_bytes
+            kern_ms = (total_ms if storage == "float32" else bf_total_ms) / args.steps
+            replication[label] = {
+                "step_ms": step_ms, "collective_only_ms": coll_ms,
+                "gsamples_per_s": workload.samples / (step_ms * 1e-3) / 1e9,
+                "received_bytes_per_rank": int(recv), "received_GBps_per_rank": recv / (coll_ms * 1e-3) / 1e9,
+                "frac_of_measured_peer_copy_770GBps": recv / (coll_ms * 1e-3) / 1e9 / 770.0,
+                "bound_by": "collective" if coll_ms > kern_ms else "kernel"}
+            if label == "all_gather_f32":
+                # the end-to-end step through host buffers: a rank uploads only its 1/N of value and its own query
+                # block; the ranks all-gather value over NVLink; the host moves one copy of the inputs in total
+                for _ in range(3):
+                    runner.step()
+                barrier()
+                t0 = time.perf_counter()
+                for _ in range(e2e_steps):
+                    e2e_out_t = runner.step()
+                barrier()
+                ms = reduce_max((time.perf_counter() - t0) * 1e3)
+                sharded_e2e = {"ms": ms, "h2d": runner.h2d_bytes, "d2h": runner.d2h_bytes,
+                               "out": e2e_out_t.numpy().copy()}
+            del runner
+        torch.cuda.synchronize()
+
+    # ---- end to end
+    if world == 1:
+        # CudaSession.run with pinned host buffers, the stripped session (no finite check, outputs returned as views)
+        graph = build_msda_graph_for(local)
+        session = CudaSession(compile_cuda(graph), device_id=local_rank, check_finite=False, fresh_outputs=False,
+                              overlap_batches=True)
+        pinned = session.pinned_inputs()
+        for name, arr in host.items():
+            np.copyto(pinned[name], arr)
+        h2d = sum(int(a.nbytes) for a in pinned.values())
+        d2h = int(out_dev.numel() * 4)
+        for _ in range(3):
+            session.run(pinned)
+        barrier()
+        t0 = time.perf_counter()
+        gpu_ms = 0.0
+        for _ in range(e2e_steps):
+            res = session.run(pinned)
+            gpu_ms += res.gpu_stream_ms
+        barrier()
+        e2e_ms = (time.perf_counter() - t0) * 1e3
+        e2e_out = res.outputs["output"]
+        session.close()
+        # the same through the session with the reference's defaults: finite check of every input and fresh host
+        # copies of the outputs (src/gac/validation/reference.py:14-29, src/gac/execution/cuda.py:441-443)
+        default_steps = max(2, min(5, e2e_steps))
+        with CudaSession(compile_cuda(graph), device_id=local_rank) as session:
+            session.run(host)
+            t0 = time.perf_counter()
+            for _ in range(default_steps):
+                session.run(host)
+            default_ms = (time.perf_counter() - t0) * 1e3 / default_steps
+        e2e_extra = {"device_ms_per_step": gpu_ms / e2e_steps,
+                     "default_session": {"ms_per_step": default_ms, "value": workload.samples / (default_ms * 1e-3) / 1e9,
+                                         "unit": UNIT, "note": "check_finite=True, fresh output copies, pageable caller arrays"}}
+        e2e_how = ("CudaSession.run, check_finite=False, fresh_outputs=False, overlap_batches=True (per-camera copy/compute/"
+                   "copy pipeline, 6 launches per step), pinned staging filled in place")
+    else:
+        e2e_ms, h2d, d2h = sharded_e2e["ms"], sharded_e2e["h2d"], sharded_e2e["d2h"]
+        e2e_out = sharded_e2e["out"]
+        e2e_extra = {"host_bytes_per_step_all_ranks": (h2d + d2h) * world, "numa_bound_cpus": len(numa_cpus) if numa_cpus else None}
+        e2e_how = ("distributed.ShardedMsda.step: per camera, each rank uploads its 1/N of the value rows and its own "
+                   "query block from pinned host memory, all-gathers the slab over NVLink, runs the kernel, copies its "
+                   "output block back; four streams")
+    e2e_gs = workload.samples * e2e_steps / (e2e_ms * 1e-3) / 1e9
+    if rank == 0:
+        from oracle import msda_c
+
+        nq = min(16, local.queries)
+        want = msda_c(host["value"], host["sampling_locations"][:, :nq], host["attention_weights"][:, :nq], local.spatial_shapes)
+        e2e_err = float(np.abs(np.asarray(e2e_out)[:, :nq] - want).max())
+        if e2e_err > 1e-4:
+            raise SystemExit(f"end-to-end parity failure in bench: max abs {e2e_err}")
 
     # DCNv2 (secondary workload): all ranks take part so that the max over ranks is a collective
     dcn_result = bench_dcn(device, world=world, rank=rank, cpu_baseline=world == 1,
@@ -749,22 +967,23 @@ def main() -> None:
         gather_peak_l2 = measure_gather_rate(device, 32)
         gather_peak_big = measure_gather_rate(device, 256)
         gather_peak_l1 = measure_gather_rate(device, 0.0625)                     # 64 KB: every line hits in L1
+        config = bench_config(workload, world)
+        config.update({"queries_per_camera_per_gpu": local.queries, "samples_per_step_per_gpu": local.samples,
+                       "l2": "inputs (435 MB per step at one GPU; the 189 MB value alone at any N) larger than L2 "
+                             "(126 MB); no flush",
+                       "e2e_path": e2e_how})
         line = {
             "metric": METRIC, "value": value_gs, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": local.name, "cameras": local.batch, "queries_per_camera_per_gpu": local.queries,
-                       "global_queries_per_camera": global_q, "levels": local.levels, "points": local.points,
-                       "heads": local.heads, "head_dim": local.head_dim, "spatial_shapes": [list(s) for s in local.spatial_shapes],
-                       "samples_per_step_per_gpu": local.samples, "sharding": f"query blocks x{world}, value replicated",
-                       "l2": "inputs (435 MB per step) larger than L2 (126 MB); no flush",
-                       "e2e_session": "check_finite=False, fresh_outputs=False, overlap_batches=True (per-camera copy/compute/copy "
-                                      "pipeline, 6 launches per step), pinned staging filled in place"},
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": config,
             "e2e": {"value": e2e_gs, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps, "device_ms_per_step": gpu_ms / e2e_steps},
+                    "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps, "checked_max_abs": e2e_err, **e2e_extra},
             "gpu_launches": args.steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": NCU_TRAFFIC_BYTES["float32"], "peak_source": f"{peak_kind} copy bandwidth",
+                         "traffic": NCU_TRAFFIC_BYTES["float32"] if world == 1 else None,
+                         "traffic_source": NCU_TRAFFIC_SOURCE if world == 1 else "not captured for a query block",
+                         "peak_source": f"{peak_kind} copy bandwidth",
                          "kernel": "msda_rows_kernel<float,4,8>", "algorithmic_bytes_per_launch": alg_bytes,
                          "avg_launch_ms": avg_launch_ms, "min_launch_ms": float(np.min(per_launch)),
                          "median_launch_ms": float(np.median(per_launch)),
@@ -775,20 +994,23 @@ def main() -> None:
                                               "random_lines_64KB_l1_resident": gather_peak_l1,
                                               "source": "gacb_gather_probe measured in this run"},
                          "gather_frac_of_l2_resident_peak": gather_bytes / (avg_launch_ms * 1e-3) / 1e9 / gather_peak_l2},
-            "bf16_value": {"value": local.samples * world * args.steps / (bf_total_ms * 1e-3) / 1e9, "unit": UNIT,
+            "bf16_value": {"value": workload.samples * args.steps / (bf_total_ms * 1e-3) / 1e9, "unit": UNIT,
                            "avg_launch_ms": bf_avg,
                            "roofline_frac": local.algorithmic_bytes(2) / (bf_avg * 1e-3) / 1e9 / peak,
-                           "traffic": NCU_TRAFFIC_BYTES["bfloat16"]},
+                           "traffic": NCU_TRAFFIC_BYTES["bfloat16"] if world == 1 else None},
             "clocks": clock_summary,
             "parity": parity,
             "value_broadcast_ms": bcast_ms,
         }
+        if replication is not None:
+            line["with_value_replication"] = replication
         line["dcnv2"] = dcn_result
         if world == 1:
             line["other_msda"] = bench_other_msda(device)
         if world == 1 and not args.no_cpu_baseline:
-            rate, times, desc, threads = cpu_reference_throughput(local, 20.0, 2, 1)
-            line["cpu_baseline"] = {"value": rate / 1e9, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc}
+            r = cpu_reference_throughput(workload, 15.0, 2, 1, single_thread_seconds=8.0)
+            line["cpu_baseline"] = {"value": r["rate"] / 1e9, "unit": UNIT, "cores": r["cores"], "kind": r["kind"],
+                                    "sample": r["sample"], "single_thread_cli_loop": r.get("single_thread")}
         else:
             line["cpu_baseline"] = None
         print(json.dumps(line), flush=True)

@@ -68,7 +68,7 @@ class CudaProgram:
             "artifact_kind": "precompiled-sm100a-library-with-launch-metadata",
             "device_code_compiled": True,
             "precision": "float32 accumulate; optional bfloat16 value storage (MSDA); "
-                         "3xTF32 / TF32 / BF16 tensor-core products (DCNv2)",
+                         "bf16 hi+lo pairs (three products, fp32-faithful) / TF32 / BF16 tensor-core products (DCNv2)",
             "name": g.name,
             "inputs": {k: s.to_dict() for k, s in g.inputs.items()},
             "outputs": {k: g.value_specs[k].to_dict() for k in g.outputs},

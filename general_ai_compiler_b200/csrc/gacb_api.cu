@@ -48,3 +48,19 @@ GACB_API int gacb_device_capability(int device) {
   }
   return major * 10 + minor;
 }
+
+GACB_API int gacb_status_from_word(int32_t word) {
+  if (word == 0) return GACB_OK;
+  return gacb::fail(GACB_ERR_DEVICE_TIMEOUT,
+                    "a kernel gave up a bounded wait (device status word = %d); its output is incomplete", (int)word);
+}
+
+GACB_API int gacb_read_status_word(const int32_t *status_word, void *stream) {
+  if (!status_word) return gacb::fail(GACB_ERR_INVALID_ARGUMENT, "read_status_word: status_word is NULL");
+  int32_t word = 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemcpyAsync(&word, status_word, sizeof(word), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) return gacb::check_cuda(e, "read_status_word");
+  return gacb_status_from_word(word);
+}

@@ -30,6 +30,8 @@
 // The grid runs rows in (batch, query, head) order, so at any moment the
 // resident CTAs gather from one batch entry's value slab, which is what keeps
 // that slab L2-resident (one BEVFormer-base camera is 31.6 MB in fp32).
+#include <mutex>
+
 #include "gacb_common.cuh"
 
 namespace gacb {
@@ -552,8 +554,14 @@ __global__ void cast_f32_to_bf16_kernel(const float *__restrict__ src, __nv_bflo
     dst[i] = __float2bfloat16_rn(src[i]);
 }
 
-template <typename VT, int CPL, int LPR, bool FUSED>
-int launch_rows(MsdaArgs &a, cudaStream_t stream) {
+// Launch shape of the rows kernel for one problem: fills the chunking fields of `a`, returns the geometry.
+struct RowsGeometry {
+  int grid, threads, rows_per_cta;
+  size_t smem;
+};
+
+template <typename VT, int LPR>
+RowsGeometry plan_rows(MsdaArgs &a) {
   constexpr int kThreads = RowsCta<VT>::kThreads;
   constexpr int RPI = kThreads / LPR;
   constexpr int kEntriesPerCta = kThreads * kRecordsPerThread;
@@ -569,26 +577,45 @@ int launch_rows(MsdaArgs &a, cudaStream_t stream) {
     a.rows_per_group = 1;
   }
   a.div_chunk_pad.set((uint32_t)a.chunk_pad);
-  const int rows_cta = RPI * a.rows_per_group;
-  const size_t smem = kMaxLevels * sizeof(int4) +
-                      (size_t)rows_cta * ((a.chunk_pad + 1) * (sizeof(float4) + sizeof(uint32_t)) + sizeof(int) + sizeof(float2));
+  RowsGeometry g;
+  g.threads = kThreads;
+  g.rows_per_cta = RPI * a.rows_per_group;
+  g.smem = kMaxLevels * sizeof(int4) +
+           (size_t)g.rows_per_cta * ((a.chunk_pad + 1) * (sizeof(float4) + sizeof(uint32_t)) + sizeof(int) + sizeof(float2));
+  g.grid = (a.total_rows + g.rows_per_cta - 1) / g.rows_per_cta;
+  return g;
+}
+
+// Per-device "attributes are set" flags of one kernel instantiation; calls may come from several host threads.
+struct OncePerDevice {
+  std::mutex lock;
+  bool done[64] = {};
+};
+
+template <typename VT, int CPL, int LPR, bool FUSED>
+int launch_rows(MsdaArgs &a, cudaStream_t stream) {
+  const RowsGeometry g = plan_rows<VT, LPR>(a);
   auto kernel = msda_rows_kernel<VT, CPL, LPR, FUSED>;
   // Once per device: allow the largest record table and ask for a shared-memory
   // carve-out that leaves most of the 256 KB to L1, where coarse-level taps hit.
-  static bool configured[64] = {};
+  static OncePerDevice once;
   int device = 0;
-  cudaGetDevice(&device);
-  if (device >= 0 && device < 64 && !configured[device]) {
-    int rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024),
-                        "cudaFuncSetAttribute(max dynamic shared memory)");
-    if (rc != GACB_OK) return rc;
-    rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, kCarveoutPercent),
-                    "cudaFuncSetAttribute(carve-out)");
-    if (rc != GACB_OK) return rc;
-    configured[device] = true;
+  int rc = check_cuda(cudaGetDevice(&device), "cudaGetDevice");
+  if (rc != GACB_OK) return rc;
+  if (device < 0 || device >= 64) return fail(GACB_ERR_UNSUPPORTED, "msda: device ordinal %d is out of range", device);
+  {
+    std::lock_guard<std::mutex> guard(once.lock);
+    if (!once.done[device]) {
+      rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024),
+                      "cudaFuncSetAttribute(max dynamic shared memory)");
+      if (rc != GACB_OK) return rc;
+      rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, kCarveoutPercent),
+                      "cudaFuncSetAttribute(carve-out)");
+      if (rc != GACB_OK) return rc;
+      once.done[device] = true;
+    }
   }
-  const int grid = (a.total_rows + rows_cta - 1) / rows_cta;
-  kernel<<<grid, kThreads, smem, stream>>>(a);
+  kernel<<<g.grid, g.threads, g.smem, stream>>>(a);
   return check_cuda(cudaGetLastError(), "msda_rows_kernel launch");
 }
 
@@ -812,8 +839,19 @@ GACB_API int gacb_msda_run(const gacb_msda_desc *d, void *stream_) {
     if (d->reduce_mode == 1 && !d->visibility)
       return fail(GACB_ERR_INVALID_ARGUMENT, "msda_run: the masked average needs a visibility tensor");
     if ((d->H * d->D) % 4) return fail(GACB_ERR_UNSUPPORTED, "msda_run: the group reduction needs H*D to be a multiple of 4");
+    // The gather kernel never writes the rows that `visibility` masks out, and the plain mean reads every row.
+    if (d->reduce_mode == 2 && d->visibility)
+      return fail(GACB_ERR_INVALID_ARGUMENT,
+                  "msda_run: reduce_mode 2 (mean) cannot be combined with a visibility tensor; use reduce_mode 1");
   }
   int rc;
+  {
+    // the whole descriptor is checked before anything is enqueued
+    MsdaArgs probe{};
+    rc = fill_common(probe, d->value, d->value_dtype, d->locations, d->attention, d->out, d->spatial_hw, d->L, d->B, d->S,
+                     d->Q, d->H, d->D, d->P, d->q_begin, d->q_end);
+    if (rc != GACB_OK) return rc;
+  }
   const bool fused = d->normalizer || d->reference;
   // With a visibility tensor and scratch for the list, compact first: the gather kernel then runs dense CTAs over
   // the visible rows only.

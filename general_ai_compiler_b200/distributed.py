@@ -12,6 +12,10 @@ locations/weights only, so ranks are independent once ``value`` is replicated.
 * ``sharded_msda``: each rank computes its query block with the local kernel;
   optionally all-gathers the blocks.  The concatenation equals the single-GPU
   output bit for bit (same per-row arithmetic).
+* ``ShardedMsda``: the same sharding when ``value`` arrives S-sharded (each
+  rank uploads 1/N of it): per batch entry an all-gather (or broadcast) over
+  NVLink into each GPU's own memory, pipelined against the kernel.
+* ``bind_host_near_gpu``: NUMA placement of a rank's pinned staging buffers.
 * ``dcn_units``: (camera, output-row block) work units so that 6 cameras still
   keep 4 or 8 GPUs busy.
 
@@ -110,14 +114,14 @@ def broadcast_value(tensor, src: int = 0, group=None) -> float:
 
 
 def sharded_msda(value, locations, weights, spatial_shapes, *, gather: bool = False,
-                 compute: Callable | None = None, group=None):
+                 compute: Callable | None = None, group=None, total_queries: int | None = None):
     """Run MSDA on this rank's query block.
 
-    ``value`` is the full (replicated) tensor; ``locations``/``weights`` are the
-    FULL ``[B,Q,...]`` tensors or this rank's slice (``local_slice=True`` is
-    inferred when their Q equals the block length).  Returns this rank's block
-    ``[B, q_end-q_begin, H*D]``, or the gathered ``[B,Q,H*D]`` when ``gather``.
-    ``compute`` defaults to the CUDA kernel; tests on CPU inject a stand-in.
+    ``value`` is the full (replicated) tensor.  ``locations``/``weights`` are either the FULL ``[B,Q,...]``
+    tensors (the default: this rank's block is cut out of them) or, when ``total_queries`` is given, ALREADY this
+    rank's block of a global set of ``total_queries`` queries (its length must then equal the block length;
+    nothing is sliced).  Returns this rank's block ``[B, q_end-q_begin, H*D]``, or the gathered ``[B,Q,H*D]``
+    when ``gather``.  ``compute`` defaults to the CUDA kernel; tests on CPU inject a stand-in.
     """
     import torch
     import torch.distributed as dist
@@ -128,10 +132,17 @@ def sharded_msda(value, locations, weights, spatial_shapes, *, gather: bool = Fa
         from . import ops
 
         compute = ops.msda_forward
-    total_q = locations.shape[1]
-    q0, q1 = query_block(total_q, world, rank)
-    loc = locations[:, q0:q1].contiguous()
-    att = weights[:, q0:q1].contiguous()
+    if total_queries is None:
+        total_q = locations.shape[1]
+        q0, q1 = query_block(total_q, world, rank)
+        loc = locations[:, q0:q1].contiguous()
+        att = weights[:, q0:q1].contiguous()
+    else:
+        total_q = int(total_queries)
+        q0, q1 = query_block(total_q, world, rank)
+        if locations.shape[1] != q1 - q0 or weights.shape[1] != q1 - q0:
+            raise ValueError(f"rank {rank} owns queries [{q0},{q1}) of {total_q}; got a slice of {locations.shape[1]}")
+        loc, att = locations, weights
     block = compute(value, loc, att, spatial_shapes)
     if not gather or world == 1:
         return block
@@ -142,3 +153,231 @@ def sharded_msda(value, locations, weights, spatial_shapes, *, gather: bool = Fa
     parts = [torch.empty_like(padded) for _ in range(world)]
     dist.all_gather(parts, padded, group=group)
     return torch.cat([p[:, : e - b] for p, (b, e) in zip(parts, sizes)], dim=1)
+
+
+def bind_host_near_gpu(device_index: int) -> list[int] | None:
+    """Pin this process to the CPUs NVML reports as closest to GPU ``device_index`` (its NUMA node), so that the
+    pinned staging buffers allocated afterwards are placed in that node's memory and the host->device copies of the
+    ranks of one node do not all cross the socket interconnect.  Returns the CPU list, or None when NVML or the
+    affinity call is unavailable (nothing is changed then).  Only this process's own affinity is touched."""
+    import os
+
+    try:
+        import pynvml
+        import torch
+
+        pynvml.nvmlInit()
+        uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+        if not uuid.startswith("GPU-"):
+            uuid = "GPU-" + uuid
+        handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+        cpus = [64 * i + b for i, word in enumerate(mask) for b in range(64) if (int(word) >> b) & 1]
+        allowed = sorted(set(cpus) & os.sched_getaffinity(0))
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return allowed
+    except Exception:
+        return None
+
+
+class _NoStream:
+    """Stand-in for streams and events on a CPU-only box: everything runs in program order."""
+
+    def wait_event(self, _):
+        pass
+
+    def wait_stream(self, _):
+        pass
+
+    def synchronize(self):
+        pass
+
+
+class ShardedMsda:
+    """Query-sharded MSDA over the ranks of one node when ``value`` does NOT start out replicated.
+
+    Rank r owns queries ``query_block(Q, world, r)`` of every batch entry (locations, weights and output are
+    sliced, never replicated) and rows ``[r*Sp, (r+1)*Sp)`` of every batch entry's value slab, ``Sp =
+    ceil(S / world)`` (the last rank's rows past S are padding).  One step, batch entry by batch entry:
+
+        host shard b  --h2d stream-->  device shard b  --comm stream: all-gather-->  full slab b in this GPU's
+        own memory  --compute stream: the MSDA kernel on slab b-->  output block b  --d2h stream-->  host
+
+    so entry b+1 is on the wire while the kernel gathers from entry b.  The all-gather output is rank-major, i.e.
+    the first S rows of the ``[world*Sp, H, D]`` buffer ARE the slab in order; the kernel reads only this GPU's
+    own memory (no peer loads).  ``replicate="broadcast"`` instead has rank 0 hold the whole value and broadcast
+    slab after slab.  ``value_storage="bfloat16"`` casts the shard on the device before it travels, halving the
+    bytes on the wire; the kernel then reads bf16 texels and accumulates in float32.
+
+    The reference runs one device (``src/gac/execution/cuda.py:132-138``): there is no behaviour to match beyond
+    "the concatenated blocks equal the single-device output", which holds bit for bit in float32.
+
+    ``compute(value[1,S,H,D], loc[1,q,...], attn[1,q,...], spatial_shapes, out[1,q,H*D])`` defaults to the CUDA
+    kernel; CPU tests inject a stand-in and run over gloo.
+    """
+
+    def __init__(self, *, batch: int, spatial_shapes, queries: int, heads: int, head_dim: int, points: int,
+                 device, value_storage: str = "float32", replicate: str = "all_gather", group=None,
+                 compute: Callable | None = None) -> None:
+        import torch
+        import torch.distributed as dist
+
+        if replicate not in ("all_gather", "broadcast"):
+            raise ValueError("replicate must be 'all_gather' or 'broadcast'")
+        if value_storage not in ("float32", "bfloat16"):
+            raise ValueError("value_storage must be 'float32' or 'bfloat16'")
+        self.torch, self.dist, self.group = torch, dist, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.device = torch.device(device)
+        self.shapes = tuple((int(h), int(w)) for h, w in spatial_shapes)
+        self.B, self.Q, self.H, self.D, self.P, self.L = batch, queries, heads, head_dim, points, len(self.shapes)
+        self.S = sum(h * w for h, w in self.shapes)
+        self.rows = -(-self.S // self.world)                    # Sp: value rows per rank and batch entry
+        self.s0 = min(self.S, self.rank * self.rows)
+        self.s1 = min(self.S, self.s0 + self.rows)
+        self.q0, self.q1 = query_block(self.Q, self.world, self.rank)
+        self.replicate = replicate
+        self.storage = torch.float32 if value_storage == "float32" else torch.bfloat16
+        self._compute = compute
+        cuda = self.device.type == "cuda"
+        qc = self.q1 - self.q0
+        dev = dict(device=self.device)
+        self.shard32 = torch.zeros((batch, self.rows, heads, head_dim), dtype=torch.float32, **dev)
+        self.shard = self.shard32 if self.storage == torch.float32 else torch.zeros_like(self.shard32, dtype=self.storage)
+        self.slabs = torch.zeros((batch, self.world * self.rows, heads, head_dim), dtype=self.storage, **dev)
+        self.loc = torch.empty((batch, qc, heads, self.L, points, 2), dtype=torch.float32, **dev)
+        self.attn = torch.empty((batch, qc, heads, self.L, points), dtype=torch.float32, **dev)
+        self.out = torch.empty((batch, qc, heads * head_dim), dtype=torch.float32, **dev)
+        pin = (lambda t: t.pin_memory()) if cuda else (lambda t: t)
+        self.host = {"value_shard": pin(torch.zeros((batch, self.rows, heads, head_dim), dtype=torch.float32)),
+                     "sampling_locations": pin(torch.empty(self.loc.shape, dtype=torch.float32)),
+                     "attention_weights": pin(torch.empty(self.attn.shape, dtype=torch.float32)),
+                     "output": pin(torch.empty(self.out.shape, dtype=torch.float32))}
+        if cuda:
+            with torch.cuda.device(self.device):
+                self.s_h2d, self.s_comm, self.s_compute, self.s_d2h = (torch.cuda.Stream() for _ in range(4))
+        else:
+            self.s_h2d = self.s_comm = self.s_compute = self.s_d2h = _NoStream()
+
+    # ---- what moves per step (for the end-to-end byte counts)
+    @property
+    def h2d_bytes(self) -> int:
+        return sum(int(self.host[k].numel()) * 4 for k in ("value_shard", "sampling_locations", "attention_weights"))
+
+    @property
+    def d2h_bytes(self) -> int:
+        return int(self.host["output"].numel()) * 4
+
+    @property
+    def wire_bytes_in(self) -> int:
+        """Bytes this rank receives over NVLink per step (all-gather: the other ranks' shards)."""
+        item = 4 if self.storage == self.torch.float32 else 2
+        slab = self.B * self.rows * self.H * self.D * item
+        return slab * (self.world - 1)
+
+    def load_host(self, value, locations, weights) -> None:
+        """Fill the pinned staging buffers with this rank's share of full host arrays (test / bench set-up)."""
+        torch = self.torch
+        v = torch.as_tensor(value)
+        self.host["value_shard"].zero_()
+        self.host["value_shard"][:, : self.s1 - self.s0].copy_(v[:, self.s0:self.s1])
+        self.host["sampling_locations"].copy_(torch.as_tensor(locations)[:, self.q0:self.q1])
+        self.host["attention_weights"].copy_(torch.as_tensor(weights)[:, self.q0:self.q1])
+
+    def upload(self) -> None:
+        """Host staging -> device, all at once (for the device-resident timing of ``step_resident``)."""
+        self.shard32.copy_(self.host["value_shard"])
+        self.loc.copy_(self.host["sampling_locations"])
+        self.attn.copy_(self.host["attention_weights"])
+        if self.device.type == "cuda":
+            self.torch.cuda.synchronize(self.device)
+
+    # ---- pieces of the pipeline
+    def _ctx(self, stream):
+        if self.device.type == "cuda":
+            return self.torch.cuda.stream(stream)
+        import contextlib
+
+        return contextlib.nullcontext()
+
+    def _event(self, stream):
+        if self.device.type != "cuda":
+            return None
+        ev = self.torch.cuda.Event()
+        ev.record(stream)
+        return ev
+
+    def set_broadcast_source(self, value) -> None:
+        """``replicate="broadcast"``: rank 0 keeps the whole value in its slab buffer (in storage dtype)."""
+        if self.rank == 0:
+            self.slabs[:, : self.S].copy_(self.torch.as_tensor(value).to(self.device).to(self.storage))
+
+    def _replicate_entry(self, b: int) -> None:
+        """Enqueue on the comm stream: slab b of every rank's own memory <- the ranks' shards (or rank 0's slab)."""
+        torch, dist = self.torch, self.dist
+        with self._ctx(self.s_comm):
+            if self.replicate == "broadcast":
+                if self.world > 1:
+                    dist.broadcast(self.slabs[b, : self.S], src=0, group=self.group)
+                return
+            if self.storage != torch.float32:
+                if self.device.type == "cuda":
+                    from . import native
+
+                    rc = native.load().gacb_cast_f32_to_bf16(self.shard32[b].data_ptr(), self.shard[b].data_ptr(),
+                                                             self.shard32[b].numel(), int(self.s_comm.cuda_stream))
+                    native.check(rc, "gacb_cast_f32_to_bf16")
+                else:
+                    self.shard[b].copy_(self.shard32[b])
+            if self.world > 1:
+                dist.all_gather_into_tensor(self.slabs[b], self.shard[b], group=self.group)
+            else:
+                self.slabs[b].copy_(self.shard[b], non_blocking=True)
+
+    def _compute_entry(self, b: int) -> None:
+        value = self.slabs[b, : self.S].unsqueeze(0)
+        loc, attn, out = self.loc[b:b + 1], self.attn[b:b + 1], self.out[b:b + 1]
+        if loc.shape[1] == 0:
+            return
+        if self._compute is not None:
+            self._compute(value, loc, attn, self.shapes, out)
+            return
+        from . import ops
+
+        ops.msda_forward(value, loc, attn, self.shapes, out=out, stream=self.s_compute)
+
+    def step_resident(self) -> None:
+        """One step with the shards (or, for ``broadcast``, rank 0's whole value) already on the device:
+        replication of entry b+1 overlaps the kernel of entry b.  Returns after enqueueing."""
+        self.s_comm.wait_stream(self.s_compute)      # the previous step's kernels still read the slabs
+        for b in range(self.B):
+            self._replicate_entry(b)
+            self.s_compute.wait_event(self._event(self.s_comm))
+            self._compute_entry(b)
+
+    def step(self):
+        """One end-to-end step from the pinned host buffers ``self.host[...]`` to ``self.host['output']``
+        (a torch tensor; valid until the next step).  Waits for the step to finish."""
+        h = self.host
+        self.s_h2d.wait_stream(self.s_comm)          # shard buffers are free once the previous gathers are done
+        self.s_h2d.wait_stream(self.s_compute)
+        self.s_comm.wait_stream(self.s_compute)
+        for b in range(self.B):
+            with self._ctx(self.s_h2d):
+                self.shard32[b].copy_(h["value_shard"][b], non_blocking=True)
+                self.loc[b].copy_(h["sampling_locations"][b], non_blocking=True)
+                self.attn[b].copy_(h["attention_weights"][b], non_blocking=True)
+            self.s_comm.wait_event(self._event(self.s_h2d))
+            self._replicate_entry(b)
+            self.s_compute.wait_event(self._event(self.s_comm))
+            self.s_compute.wait_event(self._event(self.s_h2d))
+            self._compute_entry(b)
+            self.s_d2h.wait_event(self._event(self.s_compute))
+            with self._ctx(self.s_d2h):
+                h["output"][b].copy_(self.out[b], non_blocking=True)
+        self.s_d2h.synchronize()
+        return h["output"]

@@ -24,7 +24,7 @@ class EvaluationError(GACError):
 
 
 class PassError(GACError):
-    """Kept for API compatibility; this package runs no optimisation passes."""
+    """A graph pass (``passes.fuse_deformable_sampling``) met a sub-graph it cannot rewrite consistently."""
 
 
 class BackendError(GACError):

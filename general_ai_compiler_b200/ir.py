@@ -1,9 +1,19 @@
 """Graph types of the host API: ``TensorSpec``, ``Node``, ``Graph``.
 
-They carry the same fields and validation rules as GAC's canonical graph
-(``src/gac/core/ir.py:60-120`` TensorSpec, ``:122-178`` Node, ``:180-300``
-Graph) restricted to what the deformable-sampling path needs: static or
-symbolic dimensions, named values, topological order, JSON round trip.
+The names, fields and JSON keys are those of GAC's canonical graph
+(``src/gac/core/ir.py``: ``TensorSpec`` :60, ``Node`` :122, ``Graph`` :180), so
+a graph serialised by either side loads on the other.  The checks are written
+from that contract:
+
+* a dimension is a non-negative integer, a non-empty symbol, or ``None``;
+* every name (graph, value, node id, op) is a non-empty string;
+* a node has at least one output and names each output once;
+* a graph is in static single assignment form and topological order: a value
+  is defined exactly once (as an input, a constant or a node output) before
+  its first use, and every graph output is defined;
+* ``value_specs`` may only describe values the graph defines.
+
+Everything that breaks a rule raises ``ValidationError``.
 """
 
 from __future__ import annotations
@@ -11,7 +21,7 @@ from __future__ import annotations
 import copy
 import json
 from dataclasses import dataclass, field
-from typing import Any, Mapping, Union
+from typing import Any, Iterable, Mapping, Union
 
 import numpy as np
 
@@ -21,33 +31,43 @@ Dim = Union[int, str, None]
 SCHEMA_VERSION = 1
 
 
-def _dim(d: object) -> Dim:
-    if d is None:
-        return None
-    if isinstance(d, bool):
-        raise ValidationError("a tensor dimension cannot be a boolean")
-    if isinstance(d, (int, np.integer)):
-        if int(d) < 0:
-            raise ValidationError(f"tensor dimensions must be non-negative, got {int(d)}")
-        return int(d)
-    if isinstance(d, str) and d:
+def _require(ok: bool, message: str) -> None:
+    if not ok:
+        raise ValidationError(message)
+
+
+def _is_name(value: object) -> bool:
+    return isinstance(value, str) and value != ""
+
+
+def _names(values: Iterable, what: str) -> tuple:
+    out = tuple(values)
+    for v in out:
+        _require(_is_name(v), f"{what}: {v!r} is not a non-empty string")
+    return out
+
+
+def _canonical_dim(d: object) -> Dim:
+    if d is None or _is_name(d):
         return d
-    raise ValidationError(f"bad tensor dimension {d!r}: want a non-negative int, a symbol or None")
+    integral = isinstance(d, (int, np.integer)) and not isinstance(d, (bool, np.bool_))
+    _require(integral and int(d) >= 0, f"dimension {d!r} is neither a non-negative integer, a symbol nor None")
+    return int(d)
 
 
-def _plain(v: Any) -> Any:
-    """NumPy scalars/arrays and tuples → JSON-friendly Python values."""
-    if isinstance(v, np.ndarray):
-        return v.tolist()
+def _jsonable(v: Any) -> Any:
+    """Attribute / metadata values as plain JSON types (NumPy scalars and arrays unwrapped, tuples as lists)."""
+    if v is None or isinstance(v, (str, bool, int, float)):
+        return v
     if isinstance(v, np.generic):
         return v.item()
+    if isinstance(v, np.ndarray):
+        return v.tolist()
     if isinstance(v, Mapping):
-        return {str(k): _plain(x) for k, x in v.items()}
-    if isinstance(v, (list, tuple)):
-        return [_plain(x) for x in v]
-    if v is None or isinstance(v, (str, int, float, bool)):
-        return v
-    raise ValidationError(f"attribute of type {type(v).__name__} cannot be serialised")
+        return {str(key): _jsonable(item) for key, item in v.items()}
+    if isinstance(v, (tuple, list)):
+        return [_jsonable(item) for item in v]
+    raise ValidationError(f"a value of type {type(v).__name__} has no JSON form")
 
 
 @dataclass(frozen=True)
@@ -60,13 +80,12 @@ class TensorSpec:
 
     def __post_init__(self) -> None:
         try:
-            name = np.dtype(self.dtype).name
+            dtype_name = np.dtype(self.dtype).name
         except TypeError as exc:
-            raise ValidationError(f"unsupported dtype {self.dtype!r}") from exc
-        if not isinstance(self.layout, str) or not self.layout:
-            raise ValidationError("tensor layout must be a non-empty string")
-        object.__setattr__(self, "shape", tuple(_dim(d) for d in self.shape))
-        object.__setattr__(self, "dtype", name)
+            raise ValidationError(f"{self.dtype!r} does not name a NumPy dtype") from exc
+        _require(_is_name(self.layout), "the layout tag of a tensor is a non-empty string")
+        object.__setattr__(self, "dtype", dtype_name)
+        object.__setattr__(self, "shape", tuple(map(_canonical_dim, self.shape)))
 
     @property
     def rank(self) -> int:
@@ -74,21 +93,15 @@ class TensorSpec:
 
     @property
     def is_static(self) -> bool:
-        return all(isinstance(d, int) for d in self.shape)
+        return all(type(d) is int for d in self.shape)
 
     @property
     def numel(self):
-        if not self.is_static:
-            return None
-        n = 1
-        for d in self.shape:
-            n *= d
-        return n
+        return int(np.prod(self.shape, dtype=np.int64)) if self.is_static else None
 
     @property
     def nbytes(self):
-        n = self.numel
-        return None if n is None else n * np.dtype(self.dtype).itemsize
+        return self.numel * np.dtype(self.dtype).itemsize if self.is_static else None
 
     def to_dict(self) -> dict:
         return {"shape": list(self.shape), "dtype": self.dtype, "layout": self.layout}
@@ -97,8 +110,8 @@ class TensorSpec:
     def from_dict(cls, data: Mapping[str, Any]) -> "TensorSpec":
         try:
             return cls(tuple(data["shape"]), data["dtype"], data.get("layout", "contiguous"))
-        except (KeyError, TypeError) as exc:
-            raise ValidationError(f"invalid tensor spec: {data!r}") from exc
+        except (KeyError, TypeError, AttributeError) as exc:
+            raise ValidationError(f"not a tensor spec: {data!r}") from exc
 
 
 @dataclass(frozen=True)
@@ -113,36 +126,33 @@ class Node:
     source_nodes: tuple = ()
 
     def __post_init__(self) -> None:
-        if not isinstance(self.id, str) or not self.id:
-            raise ValidationError("node id must be a non-empty string")
-        if not isinstance(self.op, str) or not self.op:
-            raise ValidationError(f"node {self.id!r} has an invalid op name")
-        ins, outs = tuple(self.inputs), tuple(self.outputs)
-        if any(not isinstance(n, str) or not n for n in ins):
-            raise ValidationError(f"node {self.id!r} has an invalid input name")
-        if not outs or any(not isinstance(n, str) or not n for n in outs):
-            raise ValidationError(f"node {self.id!r} must have named outputs")
-        if len(set(outs)) != len(outs):
-            raise ValidationError(f"node {self.id!r} defines an output more than once")
-        src = tuple(self.source_nodes) or (self.id,)
-        if any(not isinstance(s, str) or not s for s in src):
-            raise ValidationError(f"node {self.id!r} has invalid provenance")
-        object.__setattr__(self, "inputs", ins)
-        object.__setattr__(self, "outputs", outs)
-        object.__setattr__(self, "attrs", dict(self.attrs))
-        object.__setattr__(self, "source_nodes", src)
+        _require(_is_name(self.id), f"a node id is a non-empty string, got {self.id!r}")
+        where = f"node {self.id!r}"
+        _require(_is_name(self.op), f"{where}: the op is a non-empty string, got {self.op!r}")
+        frozen = {
+            "inputs": _names(self.inputs, f"{where} inputs"),
+            "outputs": _names(self.outputs, f"{where} outputs"),
+            # provenance: the nodes of the original graph this one stands for (itself unless a pass merged some)
+            "source_nodes": _names(self.source_nodes, f"{where} source_nodes") or (self.id,),
+            "attrs": dict(self.attrs),
+        }
+        outs = frozen["outputs"]
+        _require(len(outs) > 0, f"{where}: at least one output is needed")
+        _require(len(set(outs)) == len(outs), f"{where}: an output name appears twice in {list(outs)}")
+        for key, value in frozen.items():
+            object.__setattr__(self, key, value)
 
     def to_dict(self) -> dict:
         return {"id": self.id, "op": self.op, "inputs": list(self.inputs), "outputs": list(self.outputs),
-                "attrs": _plain(self.attrs), "source_nodes": list(self.source_nodes)}
+                "attrs": _jsonable(self.attrs), "source_nodes": list(self.source_nodes)}
 
     @classmethod
     def from_dict(cls, data: Mapping[str, Any]) -> "Node":
         try:
             return cls(data["id"], data["op"], tuple(data.get("inputs", ())), tuple(data["outputs"]),
                        dict(data.get("attrs", {})), tuple(data.get("source_nodes", ())))
-        except (KeyError, TypeError) as exc:
-            raise ValidationError(f"invalid node: {data!r}") from exc
+        except (KeyError, TypeError, AttributeError) as exc:
+            raise ValidationError(f"not a node: {data!r}") from exc
 
 
 @dataclass
@@ -161,72 +171,72 @@ class Graph:
         self.inputs = dict(self.inputs)
         self.outputs = tuple(self.outputs)
         self.nodes = list(self.nodes)
-        self.constants = {k: np.asarray(v) for k, v in self.constants.items()}
-        self.value_specs = dict(self.value_specs)
+        self.constants = {name: np.asarray(array) for name, array in self.constants.items()}
         self.metadata = copy.deepcopy(dict(self.metadata))
-        for k, spec in self.inputs.items():
-            self.value_specs.setdefault(k, spec)
-        for k, arr in self.constants.items():
-            self.value_specs.setdefault(k, TensorSpec(tuple(arr.shape), arr.dtype))
+        # inputs and constants describe themselves unless the caller already gave a spec
+        specs = {name: TensorSpec(array.shape, array.dtype) for name, array in self.constants.items()}
+        specs.update(self.inputs)
+        specs.update(self.value_specs)
+        self.value_specs = specs
 
     def clone(self) -> "Graph":
-        return Graph(self.name, dict(self.inputs), self.outputs, list(self.nodes),
-                     {k: v.copy() for k, v in self.constants.items()}, dict(self.value_specs),
-                     copy.deepcopy(self.metadata))
+        """A graph that shares no mutable state with this one (nodes and specs are immutable and shared)."""
+        constants = {name: array.copy() for name, array in self.constants.items()}
+        return Graph(self.name, self.inputs, self.outputs, self.nodes, constants, self.value_specs, self.metadata)
+
+    def _definitions(self) -> dict:
+        """value name -> what defines it ("input", "constant" or "node <id>"); raises on a second definition."""
+        table: dict = {}
+
+        def define(value: object, by: str) -> None:
+            _require(_is_name(value), f"graph {self.name!r}: {by} defines {value!r}, which is not a non-empty string")
+            _require(value not in table, f"graph {self.name!r}: {value!r} is defined by {table.get(value)} and again by {by}")
+            table[value] = by
+
+        for value in self.inputs:
+            define(value, "input")
+        for value in self.constants:
+            define(value, "constant")
+        ids = set()
+        for node in self.nodes:
+            _require(isinstance(node, Node), f"graph {self.name!r}: {node!r} is not a Node")
+            _require(node.id not in ids, f"graph {self.name!r}: two nodes share the id {node.id!r}")
+            ids.add(node.id)
+            for value in node.inputs:   # topological order: operands exist before the node that reads them
+                _require(value in table, f"graph {self.name!r}: node {node.id!r} reads {value!r} before anything defines it")
+            for value in node.outputs:
+                define(value, f"node {node.id!r}")
+        return table
 
     def validate(self) -> None:
-        """Names unique, every use defined earlier, every output defined, specs present."""
-        if not isinstance(self.name, str) or not self.name:
-            raise ValidationError("graph name must be a non-empty string")
-        if not self.outputs:
-            raise ValidationError(f"graph {self.name!r} must expose at least one output")
-        defined: set = set()
-        for k, spec in self.inputs.items():
-            if not isinstance(k, str) or not k:
-                raise ValidationError("graph input names must be non-empty strings")
-            if not isinstance(spec, TensorSpec):
-                raise ValidationError(f"input {k!r} does not have a TensorSpec")
-            defined.add(k)
-        for k in self.constants:
-            if not isinstance(k, str) or not k:
-                raise ValidationError("constant names must be non-empty strings")
-            if k in defined:
-                raise ValidationError(f"value {k!r} is both an input and a constant")
-            defined.add(k)
-        seen_ids: set = set()
-        for node in self.nodes:
-            if not isinstance(node, Node):
-                raise ValidationError("graph nodes must be Node objects")
-            if node.id in seen_ids:
-                raise ValidationError(f"node id {node.id!r} is used more than once")
-            seen_ids.add(node.id)
-            for use in node.inputs:
-                if use not in defined:
-                    raise ValidationError(f"node {node.id!r} uses {use!r} before its definition")
-            for out in node.outputs:
-                if out in defined:
-                    raise ValidationError(f"value {out!r} is defined more than once")
-                defined.add(out)
-        for out in self.outputs:
-            if out not in defined:
-                raise ValidationError(f"graph output {out!r} is never defined")
-        for k, spec in self.value_specs.items():
-            if k not in defined:
-                raise ValidationError(f"value_specs names unknown value {k!r}")
-            if not isinstance(spec, TensorSpec):
-                raise ValidationError(f"value {k!r} does not have a TensorSpec")
+        """Check the rules in the module docstring; returns None or raises ``ValidationError``."""
+        _require(_is_name(self.name), f"a graph name is a non-empty string, got {self.name!r}")
+        _require(len(self.outputs) > 0, f"graph {self.name!r} has no outputs")
+        table = self._definitions()
+        for value in self.outputs:
+            _require(value in table, f"graph {self.name!r}: output {value!r} is not defined by any input, constant or node")
+        typed = dict(self.inputs)
+        typed.update(self.value_specs)
+        for value, spec in typed.items():
+            _require(isinstance(spec, TensorSpec), f"graph {self.name!r}: the spec of {value!r} is not a TensorSpec")
+            _require(value in table, f"graph {self.name!r}: value_specs describes {value!r}, which the graph never defines")
 
     def to_dict(self) -> dict:
+        def constant(array: np.ndarray) -> dict:
+            return {"dtype": array.dtype.name, "shape": list(array.shape), "data": array.tolist()}
+
+        def specs(table: Mapping[str, TensorSpec]) -> dict:
+            return {name: spec.to_dict() for name, spec in table.items()}
+
         return {
             "schema_version": SCHEMA_VERSION,
             "name": self.name,
-            "inputs": {k: s.to_dict() for k, s in self.inputs.items()},
+            "inputs": specs(self.inputs),
             "outputs": list(self.outputs),
-            "nodes": [n.to_dict() for n in self.nodes],
-            "constants": {k: {"dtype": v.dtype.name, "shape": list(v.shape), "data": v.tolist()}
-                          for k, v in self.constants.items()},
-            "value_specs": {k: s.to_dict() for k, s in self.value_specs.items()},
-            "metadata": _plain(self.metadata),
+            "nodes": [node.to_dict() for node in self.nodes],
+            "constants": {name: constant(array) for name, array in self.constants.items()},
+            "value_specs": specs(self.value_specs),
+            "metadata": _jsonable(self.metadata),
         }
 
     def to_json(self) -> str:
@@ -234,19 +244,24 @@ class Graph:
 
     @classmethod
     def from_dict(cls, data: Mapping[str, Any]) -> "Graph":
+        version = data.get("schema_version", SCHEMA_VERSION) if isinstance(data, Mapping) else None
+        _require(version == SCHEMA_VERSION, f"graph schema version {version!r} is not {SCHEMA_VERSION}")
         try:
-            if data.get("schema_version", SCHEMA_VERSION) != SCHEMA_VERSION:
-                raise ValidationError(f"unsupported graph schema {data.get('schema_version')!r}")
-            consts = {k: np.asarray(c["data"], dtype=c["dtype"]).reshape(c["shape"])
-                      for k, c in data.get("constants", {}).items()}
-            g = cls(data["name"], {k: TensorSpec.from_dict(s) for k, s in data["inputs"].items()},
-                    tuple(data["outputs"]), [Node.from_dict(n) for n in data["nodes"]], consts,
-                    {k: TensorSpec.from_dict(s) for k, s in data.get("value_specs", {}).items()},
-                    dict(data.get("metadata", {})))
-        except (KeyError, TypeError) as exc:
-            raise ValidationError(f"invalid graph: {exc}") from exc
-        g.validate()
-        return g
+            constants = {name: np.asarray(entry["data"], dtype=entry["dtype"]).reshape(entry["shape"])
+                         for name, entry in data.get("constants", {}).items()}
+            graph = cls(
+                name=data["name"],
+                inputs={name: TensorSpec.from_dict(spec) for name, spec in data["inputs"].items()},
+                outputs=tuple(data["outputs"]),
+                nodes=[Node.from_dict(node) for node in data["nodes"]],
+                constants=constants,
+                value_specs={name: TensorSpec.from_dict(spec) for name, spec in data.get("value_specs", {}).items()},
+                metadata=dict(data.get("metadata", {})),
+            )
+        except (KeyError, TypeError, AttributeError, ValueError) as exc:
+            raise ValidationError(f"not a graph: {exc}") from exc
+        graph.validate()
+        return graph
 
     @classmethod
     def from_json(cls, text: str) -> "Graph":

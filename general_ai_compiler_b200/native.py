@@ -76,6 +76,8 @@ SIGNATURES = {
                                  + [_i] * 18 + [_vp, _sz, _vp, _vp]),
     "gacb_dcnv2_workspace_bytes": (_sz, [_i] * 16),
     "gacb_dcnv2_forward_static": (_i, [_vp] * 6 + [_i] * 18 + [_vp, _vp]),
+    "gacb_status_from_word": (_i, [ctypes.c_int32]),
+    "gacb_read_status_word": (_i, [_vp, _vp]),
     "gacb_cast_f32_to_bf16": (_i, [_vp, _vp, _sz, _vp]),
     "gacb_gather_probe": (_i, [_vp, _sz, _i, _i, _i, ctypes.c_uint32, _vp, ctypes.POINTER(_sz), _vp]),
 }

@@ -481,6 +481,9 @@ def msda_group_forward(value, locations, attention, spatial_shapes, *, group=1, 
         desc.visibility = visibility.data_ptr()
     elif reduce == "masked_average":
         raise EvaluationError("the masked average needs a visibility tensor")
+    if reduce == "mean" and visibility is not None:
+        # masked rows are never written by the gather kernel, and the plain mean reads every row
+        raise EvaluationError('reduce="mean" cannot be combined with visibility; use reduce="masked_average"')
     if (normalizer is None) != (reference is None):
         raise EvaluationError("normalizer and reference come together")
     if normalizer is not None:

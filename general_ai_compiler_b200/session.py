@@ -271,9 +271,16 @@ class CudaSession:
                 pair[1].record(self._stream)
                 event_pairs.append((pair, ev.metadata))
 
-    def _check_device_status(self) -> None:
-        if int(self._status.item()) != 0:
-            raise BackendError("a kernel reported an expired bounded wait (device status word set)")
+    def _check_device_status(self, word: int | None = None) -> None:
+        """Map the device status word to the reference's failure contract: a kernel that gave up a bounded wait
+        left incomplete outputs, so the invocation raises ``BackendError`` and the session is invalid from then on
+        (``src/gac/execution/cuda.py:457-464``).  ``word`` overrides the device read (host-side tests)."""
+        if word is None:
+            word = int(self._status.item())
+        rc = ops.native.load().gacb_status_from_word(int(word))
+        if rc != ops.native.GACB_OK:
+            self._failed = True
+            ops.native.check(rc, "device status word")
 
     def _can_overlap(self) -> bool:
         g = self.program.graph

@@ -278,6 +278,18 @@ int gacb_dcnv2_forward_static(const float *x, const float *offset, const float *
                               int deform_groups, int n_begin, int n_end, int math_mode,
                               int32_t *status_word, void *stream);
 
+/* The device status word of the calls above, turned into a status.  (GAC reports a failed device step as a
+ * `failed` session / a `status:"failed"` report with the failing stage: src/gac/execution/cuda.py:457-464,
+ * native/runtime/cuda-run.cpp:685-703.)
+ *   gacb_status_from_word   pure host function: GACB_OK for 0, else GACB_ERR_DEVICE_TIMEOUT with a message;
+ *   gacb_read_status_word   copies the word from the device on `stream`, waits for the stream (so every kernel
+ *                           enqueued before it has finished) and returns gacb_status_from_word of it.  After
+ *                           GACB_ERR_DEVICE_TIMEOUT the outputs of the calls that shared the word are incomplete;
+ *                           the context stays usable (the kernels returned by themselves) and the caller clears
+ *                           the word before reusing it. */
+int gacb_status_from_word(int32_t word);
+int gacb_read_status_word(const int32_t *status_word, void *stream);
+
 /* float32 -> bfloat16 (round to nearest even) for the bf16-storage value variant. */
 int gacb_cast_f32_to_bf16(const float *src, void *dst, size_t count, void *stream);
 

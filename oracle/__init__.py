@@ -9,6 +9,10 @@ the benchmark, and only as the checker or as the CPU arm being timed.
 ``gac_oracle.c`` C restatement of the same MSDA arithmetic and of the native
                  DCNv2 lowering (native/lib/DeviceLowering.cpp:605-698,
                  :251-286); loaded through :func:`load_c_oracle`.
+``_ref/``        (never committed) the reference's own evaluator modules, placed
+                 there by ``make_ref.py`` from a checkout; :func:`load_reference`
+                 imports them.  Used as the timed CPU arm (kind "reference") and
+                 to re-check the restatements wherever the directory exists.
 """
 
 from __future__ import annotations
@@ -152,3 +156,46 @@ def dcnv2_fused_c(x, offset, mask_logits, weight, bias, bn=None, relu=False, **c
 
 def host_threads() -> int:
     return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+
+
+_REF_DIR = _HERE / "_ref"
+_reference = None
+
+
+def reference_available() -> bool:
+    return (_REF_DIR / "gac" / "core" / "ops.py").is_file()
+
+
+def load_reference():
+    """The reference's own modules from ``oracle/_ref`` (see ``make_ref.py``) as a namespace with ``evaluate_op``,
+    ``reference_run``, ``Graph``, ``Node`` and ``TensorSpec``; raises ``FileNotFoundError`` when they are absent."""
+    global _reference
+    if _reference is None:
+        if not reference_available():
+            raise FileNotFoundError(f"{_REF_DIR} is empty: run oracle/make_ref.py on a box that has the reference checkout")
+        import importlib
+        import sys
+        from types import SimpleNamespace
+
+        sys.dont_write_bytecode = True
+        sys.path.insert(0, str(_REF_DIR))
+        try:
+            ops = importlib.import_module("gac.core.ops")
+            ir = importlib.import_module("gac.core.ir")
+            ref = importlib.import_module("gac.validation.reference")
+        finally:
+            sys.path.remove(str(_REF_DIR))
+        _reference = SimpleNamespace(evaluate_op=ops.evaluate_op, reference_run=ref.reference_run, Graph=ir.Graph,
+                                     Node=ir.Node, TensorSpec=ir.TensorSpec)
+    return _reference
+
+
+def reference_msda_graph(ref, batch, spatial_size, queries, heads, head_dim, levels, points, spatial_shapes):
+    """The one-node MSDA graph in the reference's own IR (node recipe of its tests/test_bevformer_msda.py:23-30)."""
+    spec = ref.TensorSpec
+    inputs = {"value": spec((batch, spatial_size, heads, head_dim), "float32"),
+              "sampling_locations": spec((batch, queries, heads, levels, points, 2), "float32"),
+              "attention_weights": spec((batch, queries, heads, levels, points), "float32")}
+    node = ref.Node("msda", "MSDeformableAttention", ("value", "sampling_locations", "attention_weights"), ("output",),
+                    {"spatial_shapes": [list(map(int, s)) for s in spatial_shapes]})
+    return ref.Graph("msda", inputs, ("output",), [node])

@@ -56,8 +56,8 @@ sys.path.insert(0, str(ROOT))
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("GAC_REFERENCE", "/root/reference"),
-                    help="checkout of the reference project (its src/ must be importable)")
+    ap.add_argument("--reference", default=os.environ.get("GAC_REFERENCE"), required="GAC_REFERENCE" not in os.environ,
+                    help="checkout of the reference project (its src/ must be importable); default: $GAC_REFERENCE")
     ap.add_argument("--only", default="", help="write just one fixture file: 'softmax', 'dcn_fused', 'reduce' or 'conv'")
     args = ap.parse_args()
     sys.dont_write_bytecode = True

@@ -114,3 +114,71 @@ def _worker(rank: int, world: int, port: int, tmp: str) -> None:
 def test_query_sharded_msda_over_gloo(world, tmp_path):
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     assert sorted(p.name for p in tmp_path.iterdir()) == [f"ok{r}" for r in range(world)]
+
+
+def _sharded_value_worker(rank: int, world: int, port: int, tmp: str) -> None:
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from general_ai_compiler_b200.bevformer import WORKLOADS, make_workload_inputs
+        from general_ai_compiler_b200.distributed import ShardedMsda, sharded_msda
+        from oracle import msda_c
+
+        # S = 30825 does not divide by 2 or 3 evenly for every level mix; 37 queries leave ragged blocks
+        w = WORKLOADS["base_sca"].with_queries(37)
+        x = make_workload_inputs(w)
+        whole = msda_c(x["value"], x["sampling_locations"], x["attention_weights"], w.spatial_shapes)
+
+        def compute(v, l, a, shapes, out):          # stand-in for the CUDA kernel on a CPU-only box
+            out.copy_(torch.from_numpy(msda_c(v.float().numpy(), l.numpy(), a.numpy(), shapes)))
+
+        for replicate in ("all_gather", "broadcast"):
+            runner = ShardedMsda(batch=w.batch, spatial_shapes=w.spatial_shapes, queries=w.queries, heads=w.heads,
+                                 head_dim=w.head_dim, points=w.points, device="cpu", replicate=replicate, compute=compute)
+            assert runner.rows * world >= runner.S and (runner.q0, runner.q1) == query_block(37, world, rank)
+            runner.load_host(x["value"], x["sampling_locations"], x["attention_weights"])
+            if replicate == "broadcast":
+                runner.set_broadcast_source(x["value"])
+            # a rank uploads only its rows of value: 1/world of it (rounded up) instead of all of it
+            assert runner.host["value_shard"].shape[1] == -(-w.spatial_size // world)
+            if replicate == "all_gather":
+                out = runner.step()                                   # end to end from the host staging buffers
+                assert np.array_equal(out.numpy(), whole[:, runner.q0:runner.q1])
+                # every rank now holds the whole value, assembled from the shards, in its own memory
+                assert np.array_equal(runner.slabs[:, : runner.S].numpy(), x["value"])
+            runner.out.zero_()
+            runner.upload()
+            runner.step_resident()
+            assert np.array_equal(runner.out.numpy(), whole[:, runner.q0:runner.q1]), replicate
+        # bf16 on the wire: the gathered slabs are the rounded value, the result is the oracle on that value
+        runner = ShardedMsda(batch=w.batch, spatial_shapes=w.spatial_shapes, queries=w.queries, heads=w.heads,
+                             head_dim=w.head_dim, points=w.points, device="cpu", value_storage="bfloat16", compute=compute)
+        runner.load_host(x["value"], x["sampling_locations"], x["attention_weights"])
+        out = runner.step()
+        rounded = torch.from_numpy(x["value"]).to(torch.bfloat16).float().numpy()
+        want = msda_c(rounded, x["sampling_locations"], x["attention_weights"], w.spatial_shapes)
+        assert np.array_equal(out.numpy(), want[:, runner.q0:runner.q1])
+        assert runner.wire_bytes_in == (world - 1) * w.batch * runner.rows * w.heads * w.head_dim * 2
+
+        # sharded_msda given a rank-local slice of a stated global query count
+        loc, attn = torch.from_numpy(x["sampling_locations"]), torch.from_numpy(x["attention_weights"])
+        q0, q1 = query_block(37, world, rank)
+
+        def compute3(v, l, a, shapes):
+            return torch.from_numpy(msda_c(v.numpy(), l.numpy(), a.numpy(), shapes))
+
+        full = sharded_msda(torch.from_numpy(x["value"]), loc[:, q0:q1].contiguous(), attn[:, q0:q1].contiguous(),
+                            w.spatial_shapes, gather=True, compute=compute3, total_queries=37)
+        assert np.array_equal(full.numpy(), whole)
+        with pytest.raises(ValueError):
+            sharded_msda(torch.from_numpy(x["value"]), loc, attn, w.spatial_shapes, compute=compute3, total_queries=37 * 5)
+        Path(tmp, f"ok{rank}").write_text("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_value_arrives_sharded_and_is_all_gathered(world, tmp_path):
+    mp.spawn(_sharded_value_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert sorted(p.name for p in tmp_path.iterdir()) == [f"ok{r}" for r in range(world)]

@@ -3,9 +3,8 @@
 Some hosts plan every byte of device memory before the first inference (a fixed arena, a plugin slot in another
 engine, a real-time loop that cannot afford cudaMalloc's device-wide synchronisation) and so cannot supply the
 scratch buffer ``gacb_dcnv2_forward`` asks for.  ``gacb_dcnv2_forward_static`` keeps that scratch inside the
-library.  This file is collected last on purpose: if it fails, a run that stops at the first failure has already
-exercised every other test.  It also passes when run alone in a fresh process (the first call on the device does
-the one-time address lookup).
+library.  The test does not depend on what ran before it in the process: the first call on the device does the
+one-time address lookup, whether or not other entry points were used earlier.
 """
 
 from __future__ import annotations
