@@ -723,7 +723,8 @@ def main() -> None:
 
     from general_ai_compiler_b200 import ops
     from general_ai_compiler_b200.compiler import compile_cuda
-    from general_ai_compiler_b200.distributed import ShardedMsda, bind_host_near_gpu, broadcast_value, query_block
+    from general_ai_compiler_b200.distributed import (ShardedMsda, bind_host_near_gpu, broadcast_value, head_shard,
+                                                     nccl_high_priority_options, query_block)
     from general_ai_compiler_b200.session import CudaSession
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -735,7 +736,7 @@ def main() -> None:
     torch.cuda.set_device(device)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=device)
+        dist.init_process_group("nccl", device_id=device, pg_options=nccl_high_priority_options())
 
     def barrier():
         torch.cuda.synchronize()
@@ -897,6 +898,59 @@ def main() -> None:
             del runner
         torch.cuda.synchronize()
 
+    # ---- N > 1, the other way to cut the step: by attention heads.  A rank keeps only its heads of value,
+    # locations and weights (what head-wise projections would hand it), so nothing is replicated and nothing
+    # crosses NVLink; its output is a block of columns.  Reported beside the query-block figures.
+    head_split = None
+    if world > 1 and workload.heads % world == 0:
+        full_host = make_workload_inputs(workload)
+        hv, hl, ha, (h0, h1) = head_shard(full_host["value"], full_host["sampling_locations"], full_host["attention_weights"],
+                                          world, rank)
+        del full_host
+        hw = type(workload)(workload.name, workload.batch, workload.queries, h1 - h0, workload.head_dim, workload.points,
+                            workload.spatial_shapes, workload.location_model, workload.sigma, workload.seed)
+        tv, tl, ta = (torch.from_numpy(t).to(device) for t in (hv, hl, ha))
+        tout = torch.empty((hw.batch, hw.queries, hw.heads * hw.head_dim), dtype=torch.float32, device=device)
+        for _ in range(max(3, args.warmup)):
+            ops.msda_forward(tv, tl, ta, hw.spatial_shapes, out=tout, stream=stream)
+        barrier()
+        a_ev, b_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a_ev.record(stream)
+        for _ in range(args.steps):
+            ops.msda_forward(tv, tl, ta, hw.spatial_shapes, out=tout, stream=stream)
+        b_ev.record(stream)
+        barrier()
+        hs_ms = reduce_max(a_ev.elapsed_time(b_ev) / args.steps)
+        session = CudaSession(compile_cuda(build_msda_graph_for(hw)), device_id=local_rank, check_finite=False,
+                              fresh_outputs=False, overlap_batches=True)
+        pinned = session.pinned_inputs()
+        for name, arr in (("value", hv), ("sampling_locations", hl), ("attention_weights", ha)):
+            np.copyto(pinned[name], arr)
+        for _ in range(3):
+            session.run(pinned)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            res = session.run(pinned)
+        barrier()
+        hs_e2e_ms = reduce_max((time.perf_counter() - t0) * 1e3) / e2e_steps
+        hs_err = None
+        if rank == 0:
+            from oracle import msda_c
+
+            want = msda_c(hv, hl[:, :16], ha[:, :16], hw.spatial_shapes)
+            hs_err = float(np.abs(res.outputs["output"][:, :16] - want).max())
+            if hs_err > 1e-4:
+                raise SystemExit(f"head-split parity failure in bench: max abs {hs_err}")
+        session.close()
+        head_split = {"heads_per_gpu": h1 - h0, "ms_per_step": hs_ms, "value": workload.samples / (hs_ms * 1e-3) / 1e9,
+                      "unit": UNIT, "value_bytes_per_gpu": int(hv.nbytes), "collectives": "none",
+                      "e2e": {"value": workload.samples / (hs_e2e_ms * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": hs_e2e_ms,
+                              "h2d_bytes_per_step": int(hv.nbytes + hl.nbytes + ha.nbytes),
+                              "d2h_bytes_per_step": int(tout.numel() * 4), "checked_max_abs": hs_err,
+                              "path": "CudaSession.run on the rank's heads (stripped session, per-camera pipeline)"}}
+        del tv, tl, ta, tout
+
     # ---- end to end
     if world == 1:
         # CudaSession.run with pinned host buffers, the stripped session (no finite check, outputs returned as views)
@@ -1004,6 +1058,8 @@ def main() -> None:
         }
         if replication is not None:
             line["with_value_replication"] = replication
+        if head_split is not None:
+            line["head_split"] = head_split
         line["dcnv2"] = dcn_result
         if world == 1:
             line["other_msda"] = bench_other_msda(device)

@@ -183,6 +183,30 @@ def bind_host_near_gpu(device_index: int) -> list[int] | None:
         return None
 
 
+def head_shard(value, locations, weights, world: int, rank: int):
+    """This rank's attention heads of an MSDA call: ``(value[:, :, h0:h1], locations[:, :, h0:h1], weights[:, :,
+    h0:h1], (h0, h1))`` as dense arrays (NumPy in, NumPy out; torch in, torch out).
+
+    Heads never share a texel line, a location or an output element, so a rank that holds only its heads runs the
+    unchanged kernel on ``H/world`` heads and produces columns ``[h0*D, h1*D)`` of the output -- with NOTHING
+    replicated: each rank stores, uploads and reads 1/world of ``value``.  It is the layout a head-wise
+    (column-parallel) value / offset / weight projection leaves its results in; query blocks (``query_block``)
+    need the whole ``value`` on every rank instead."""
+    heads = int(value.shape[2])
+    h0, h1 = unit_block(heads, world, rank)
+    dense = (lambda t: t.contiguous()) if hasattr(value, "contiguous") else np.ascontiguousarray
+    return dense(value[:, :, h0:h1]), dense(locations[:, :, h0:h1]), dense(weights[:, :, h0:h1]), (h0, h1)
+
+
+def nccl_high_priority_options():
+    """``pg_options`` for ``init_process_group("nccl", ...)`` that put NCCL's kernels on high-priority streams."""
+    import torch.distributed as dist
+
+    opts = dist.ProcessGroupNCCL.Options()
+    opts.is_high_priority_stream = True
+    return opts
+
+
 class _NoStream:
     """Stand-in for streams and events on a CPU-only box: everything runs in program order."""
 
@@ -216,7 +240,9 @@ class ShardedMsda:
     "the concatenated blocks equal the single-device output", which holds bit for bit in float32.
 
     ``compute(value[1,S,H,D], loc[1,q,...], attn[1,q,...], spatial_shapes, out[1,q,H*D])`` defaults to the CUDA
-    kernel; CPU tests inject a stand-in and run over gloo.
+    kernel; CPU tests inject a stand-in and run over gloo.  With NCCL, create the process group with
+    high-priority streams (``nccl_high_priority_options()``), or the collective of entry b+1 queues up behind
+    the thousands of CTAs of entry b's kernel instead of running beside them.
     """
 
     def __init__(self, *, batch: int, spatial_shapes, queries: int, heads: int, head_dim: int, points: int,
@@ -259,7 +285,10 @@ class ShardedMsda:
                      "output": pin(torch.empty(self.out.shape, dtype=torch.float32))}
         if cuda:
             with torch.cuda.device(self.device):
-                self.s_h2d, self.s_comm, self.s_compute, self.s_d2h = (torch.cuda.Stream() for _ in range(4))
+                # the collectives go first wherever they compete with a gather kernel for SMs: a kernel launched
+                # later on a stream of equal priority would wait for the earlier kernel's whole grid
+                self.s_comm = torch.cuda.Stream(priority=-1)
+                self.s_h2d, self.s_compute, self.s_d2h = (torch.cuda.Stream() for _ in range(3))
         else:
             self.s_h2d = self.s_comm = self.s_compute = self.s_d2h = _NoStream()
 

@@ -155,6 +155,17 @@ typedef struct gacb_msda_desc {
 } gacb_msda_desc;
 int gacb_msda_run(const gacb_msda_desc *desc, void *stream);
 
+/* Kernel choice for one-level "query grid = texel grid" calls (temporal self-attention over the BEV map:
+ * src/gac/models/bevformer/temporal.py:366-373).  When value is float32 with D = 32, there is one level with
+ * Q = H_0*W_0 (query q sits on texel q), L*P <= 8 and no visibility mask, the MSDA entry points above can run
+ * a kernel that stages each 16 x 16 query block's window of the value map in shared memory and gathers from there,
+ * falling back to global memory, sample by sample, for samples outside the window.  Results are bit-identical to
+ * the general kernel.  It is off by default: on B200 it trades L2 traffic (4.6 times less) for shared-memory
+ * traffic of the same volume and ends level with the general kernel.  No reference counterpart (a tuning knob):
+ *   gacb_msda_tile_path(mode)      mode 0 = never use that kernel (default), 1 = use it where it applies, any
+ *                                  other value = leave unchanged; returns the previous mode.  Process-wide. */
+int gacb_msda_tile_path(int mode);
+
 /* DCNv2 modulated deformable convolution, forward.
  *
  * Replaces: the native `gac_op_<idx>` for gac.deform_conv2d produced by

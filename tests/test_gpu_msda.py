@@ -400,3 +400,79 @@ def test_gather_probe_contract_and_launch():
     assert lib.gacb_gather_probe(None, 1024, 8, 32, 16, 1, sink.data_ptr(), None, None) == -1
     assert lib.gacb_gather_probe(buf.data_ptr(), 3 * 128, 8, 32, 16, 1, sink.data_ptr(), None, None) == -1       # not a power of two
     assert "gather probe" in native.last_error()
+
+
+def _tile_mode(mode):
+    from general_ai_compiler_b200 import native
+
+    return native.load().gacb_msda_tile_path(mode)
+
+
+@pytest.mark.parametrize("key", ["tiny_tsa", "base_tsa"])
+def test_tile_kernel_is_bit_identical_to_the_rows_kernel(key, dev):
+    """Temporal self-attention shapes (one level, queries = the level's raster) run the shared-memory tile kernel;
+    switching it off runs the general rows kernel on the same inputs.  The two must agree bit for bit, whole and
+    sharded by query ranges that start and end inside a grid row."""
+    torch, ops, device = dev
+    from general_ai_compiler_b200.bevformer import WORKLOADS, make_workload_inputs
+    from oracle import msda_c
+
+    w = WORKLOADS[key]
+    x = make_workload_inputs(w)
+    args = (x["value"], x["sampling_locations"], x["attention_weights"], w.spatial_shapes)
+    previous = _tile_mode(0)
+    try:
+        rows = _run(dev, *args)
+        _tile_mode(1)
+        tile = _run(dev, *args)
+        assert torch.equal(tile, rows)
+        assert_fp32_gate(tile.cpu().numpy(), msda_c(*args), key)
+        out = torch.full_like(rows, float("nan"))
+        q = w.queries
+        bounds = [0, 17, q // 3 + 5, q // 3 + 6, q - 1, q]
+        for q0, q1 in zip(bounds[:-1], bounds[1:]):
+            _run(dev, *args, q_range=(q0, q1), out=out)
+        assert torch.equal(out, rows)
+        part = torch.full_like(rows, 3.0)
+        _run(dev, *args, q_range=(w.queries // 2 + 3, w.queries // 2 + 40), out=part)
+        keep = torch.ones(w.queries, dtype=torch.bool, device=device)
+        keep[w.queries // 2 + 3:w.queries // 2 + 40] = False
+        assert torch.all(part[:, keep] == 3.0) and torch.equal(part[:, ~keep], rows[:, ~keep])
+    finally:
+        _tile_mode(previous)
+
+
+def test_tile_kernel_samples_far_from_their_cell_and_softmax_form(dev):
+    """Samples anywhere in (and outside) the map: most taps miss the staged window and come from global memory,
+    level extents that are not multiples of the tile, scores with the softmax in the kernel."""
+    torch, ops, device = dev
+    from oracle import msda_c
+    from oracle.msda_numpy import msda_logits_forward
+
+    rng = np.random.default_rng(77)
+    for (hh, ww), batch, points in (((37, 53), 2, 4), ((16, 16), 1, 8), ((61, 18), 3, 3)):
+        q = hh * ww
+        value = rng.standard_normal((batch, q, 8, 32)).astype(np.float32)
+        near = np.stack(np.meshgrid((np.arange(ww) + 0.5) / ww, (np.arange(hh) + 0.5) / hh, indexing="xy"), -1).reshape(1, q, 1, 1, 1, 2)
+        loc = (near + rng.standard_normal((batch, q, 8, 1, points, 2)) * 0.04).astype(np.float32)
+        far = rng.uniform(-0.2, 1.2, loc.shape).astype(np.float32)
+        loc = np.where(rng.uniform(size=(batch, q, 8, 1, points, 1)) < 0.3, far, loc).astype(np.float32)
+        logits = rng.standard_normal((batch, q, 8, 1, points)).astype(np.float32)
+        attn = rng.uniform(0, 1, logits.shape).astype(np.float32)
+        shapes = [(hh, ww)]
+        previous = _tile_mode(0)
+        try:
+            rows = _run(dev, value, loc, attn, shapes)
+            _tile_mode(1)
+            tile = _run(dev, value, loc, attn, shapes)
+            assert torch.equal(tile, rows), (hh, ww)
+            assert_fp32_gate(tile.cpu().numpy(), msda_c(value, loc, attn, shapes), f"tile {hh}x{ww}")
+            t = [torch.from_numpy(a).to(device) for a in (value, loc, logits)]
+            soft = ops.msda_forward(*t, shapes, softmax=True)
+            _tile_mode(0)
+            soft_rows = ops.msda_forward(*t, shapes, softmax=True)
+            torch.cuda.synchronize()
+            assert torch.equal(soft, soft_rows)
+            assert_fp32_gate(soft.cpu().numpy(), msda_logits_forward(value, loc, logits, shapes), f"tile softmax {hh}x{ww}")
+        finally:
+            _tile_mode(previous)

@@ -73,6 +73,24 @@ def test_dcn_pixel_blocks_are_contiguous_and_tile_aligned():
             assert max(sizes) - min(sizes) <= 2 * 128
 
 
+def test_head_shards_concatenate_to_the_whole_output():
+    from general_ai_compiler_b200.bevformer import WORKLOADS, make_workload_inputs
+    from general_ai_compiler_b200.distributed import head_shard
+    from oracle import msda_c
+
+    w = WORKLOADS["base_sca"].with_queries(23)
+    x = make_workload_inputs(w)
+    whole = msda_c(x["value"], x["sampling_locations"], x["attention_weights"], w.spatial_shapes)
+    for world in (1, 2, 3, 8):
+        parts = []
+        for rank in range(world):
+            v, l, a, (h0, h1) = head_shard(x["value"], x["sampling_locations"], x["attention_weights"], world, rank)
+            assert v.shape[2] == h1 - h0 and v.flags.c_contiguous and l.flags.c_contiguous
+            if h1 > h0:
+                parts.append(msda_c(v, l, a, w.spatial_shapes))
+        assert np.array_equal(np.concatenate(parts, axis=2), whole)
+
+
 def _free_port() -> int:
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
