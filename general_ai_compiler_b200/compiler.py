@@ -26,7 +26,6 @@ from .ops import FUSED_MSDA, MAX_LEVELS, MAX_POINTS, SUPPORTED_OPS, infer_node
 from .passes import fuse_deformable_sampling, infer_neighbour_specs
 
 TARGET = "cuda-sm100a"
-THREADS_PER_CTA = 256
 
 ENTRY_POINTS = {
     "MSDeformableAttention": "gacb_msda_forward",
@@ -96,64 +95,74 @@ def _check_specs(graph: Graph) -> None:
             raise BackendError(f"{TARGET}: constant {name!r} must contain finite values")
 
 
-def msda_rows_per_cta(head_dim: int, samples: int, value_dtype: str = "float32") -> int | None:
-    """Rows (batch, query, head) one CTA of the vector kernel covers; None = scalar fallback kernel.
+def _msda_launch(node: Node, value: TensorSpec, b: int, q: int, h: int, levels_points, shapes, storage: str):
+    """(grid, block, kernel name, rows per thread block) of the MSDA launch, asked of the library itself
+    (``gacb_msda_launch_geometry``): the kernels are precompiled, so only the library knows their shapes."""
+    from . import native
 
-    Mirrors the launch arithmetic of ``csrc/msda.cu``: CPL channels per lane
-    (4 for float32, 8 for bfloat16), LPR = D / CPL lanes per row (a power of two
-    up to 32), 256/LPR rows side by side, and up to 8 row batches per CTA while
-    the CTA's tap table (samples padded to a multiple of 4) stays within 512 records.
-    """
-    cpl = 4 if value_dtype == "float32" else 8
-    if head_dim % cpl:
-        return None
-    lpr = head_dim // cpl
-    if lpr not in (1, 2, 4, 8, 16, 32):
-        return None
-    side = THREADS_PER_CTA // lpr
-    cap = max(4, 512 // side)
-    if samples <= cap:
-        padded = -(-samples // 4) * 4
-        return side * max(1, min(8, cap // padded))
-    return side
+    l, p = levels_points
+    dtype = native.GACB_F32 if storage == "float32" else native.GACB_BF16
+    geo = native.msda_launch_geometry(dtype, shapes, b, q, h, value.shape[3], p)
+    return tuple(geo.grid), tuple(geo.block), geo.kernel.decode(), int(geo.units_per_cta)
+
+
+def msda_rows_per_cta(head_dim: int, samples: int, value_dtype: str = "float32") -> int | None:
+    """Rows (batch, query, head) one thread block of the vector kernel covers; None = one-thread-per-output kernel.
+    Answered by the library for a one-level problem with ``samples`` points."""
+    from . import native
+
+    dtype = native.GACB_F32 if value_dtype == "float32" else native.GACB_BF16
+    geo = native.msda_launch_geometry(dtype, [(1, 1)], 1, 4096, 1, head_dim, samples)
+    return int(geo.units_per_cta) if geo.kernel.startswith(b"msda_rows") else None
 
 
 def _plan(node: Node, specs: dict, options: dict) -> KernelLaunch:
+    from . import native
+
     out_spec: TensorSpec = specs[node.outputs[0]]
     if node.op == FUSED_MSDA:
         b, q, h, l, p = node.attrs["dims"]
         value = specs[node.inputs[0]]
         storage = options.get("value_storage", "float32")
-        rows = msda_rows_per_cta(value.shape[3], l * p, storage)
-        grid = (math.ceil(b * q * h / rows), 1, 1) if rows else (math.ceil(b * q * h * value.shape[3] / THREADS_PER_CTA), 1, 1)
+        grid, block, kernel, _ = _msda_launch(node, value, b, q, h, (l, p), node.attrs["spatial_shapes"], storage)
         what = [k for k in ("softmax",) if node.attrs.get(k)] + \
                (["coordinates"] if node.attrs.get("coordinates") == "offsets" else []) + \
                ([node.attrs["reduce"]] if node.attrs.get("reduce", "none") != "none" else [])
-        candidates = (f"rows-vector-{storage}+" + "+".join(what),)
-        return KernelLaunch(ENTRY_POINTS[node.op], node.id, node.inputs, node.outputs[0], grid,
-                            (THREADS_PER_CTA, 1, 1), node.source_nodes, candidates)
+        # with a visibility operand the grid is an upper bound: thread blocks past the compacted row list return
+        candidates = (kernel + ("+" + "+".join(what) if what else ""),)
+        return KernelLaunch(ENTRY_POINTS[node.op], node.id, node.inputs, node.outputs[0], grid, block,
+                            node.source_nodes, candidates)
     if node.op in ("DeformConv2D", "Conv2D"):
-        n, cout, ho, wo = out_spec.shape
-        grid = (math.ceil(n * ho * wo / 128), 1, 1)
-        candidates = ("tcgen05-implicit-gemm-" + options.get("dcn_math", "f32x3"),)
-    else:
-        value, loc = specs[node.inputs[0]], specs[node.inputs[1]]
-        b, q, h = loc.shape[0], loc.shape[1], loc.shape[2]
-        samples = loc.shape[3] * loc.shape[4]
-        if len(node.attrs["spatial_shapes"]) > MAX_LEVELS:
-            _reject(node, f"at most {MAX_LEVELS} feature levels are supported")
-        if loc.shape[4] > MAX_POINTS:
-            _reject(node, f"at most {MAX_POINTS} sampling points per level are supported")
-        storage = options.get("value_storage", "float32")
-        rows = msda_rows_per_cta(value.shape[3], samples, storage)
-        if rows is None:
-            grid = (math.ceil(b * q * h * value.shape[3] / THREADS_PER_CTA), 1, 1)
-            candidates = ("scalar-per-output",)
+        x, w = specs[node.inputs[0]], specs[node.inputs[3 if node.op == "DeformConv2D" else 1]]
+        math = native.DCN_MATH_MODES[options.get("dcn_math", "f32x3")]
+        if node.op == "DeformConv2D":
+            from .ops import dcn_attrs
+
+            stride, padding, dilation, groups, dgroups = dcn_attrs(node)
+            plain = False
         else:
-            grid = (math.ceil(b * q * h / rows), 1, 1)
-            candidates = (f"rows-vector-{storage}",)
-    return KernelLaunch(ENTRY_POINTS[node.op], node.id, node.inputs, node.outputs[0], grid,
-                        (THREADS_PER_CTA, 1, 1), node.source_nodes, candidates)
+            from .ops import conv_attrs
+
+            stride, pads, dilation, groups = conv_attrs(node)
+            padding, dgroups, plain = (pads[0], pads[1]), 1, True
+        try:
+            geo = native.dcnv2_launch_geometry(x.shape[0], x.shape[1], x.shape[2], x.shape[3], w.shape[0], w.shape[2],
+                                               w.shape[3], stride, padding, dilation, groups, dgroups, math, plain=plain)
+        except Exception as exc:
+            _reject(node, str(exc))
+        return KernelLaunch(ENTRY_POINTS[node.op], node.id, node.inputs, node.outputs[0], tuple(geo.grid),
+                            tuple(geo.block), node.source_nodes, (geo.kernel.decode(),))
+    value, loc = specs[node.inputs[0]], specs[node.inputs[1]]
+    b, q, h = loc.shape[0], loc.shape[1], loc.shape[2]
+    if len(node.attrs["spatial_shapes"]) > MAX_LEVELS:
+        _reject(node, f"at most {MAX_LEVELS} feature levels are supported")
+    if loc.shape[4] > MAX_POINTS:
+        _reject(node, f"at most {MAX_POINTS} sampling points per level are supported")
+    storage = options.get("value_storage", "float32")
+    grid, block, kernel, _ = _msda_launch(node, value, b, q, h, (loc.shape[3], loc.shape[4]),
+                                          node.attrs["spatial_shapes"], storage)
+    return KernelLaunch(ENTRY_POINTS[node.op], node.id, node.inputs, node.outputs[0], grid, block,
+                        node.source_nodes, (kernel,))
 
 
 def compile_cuda(graph: Graph, *, fuse: bool = True, value_storage: str = "float32",

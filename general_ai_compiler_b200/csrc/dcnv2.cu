@@ -1072,6 +1072,54 @@ __global__ void __launch_bounds__(CtaShape<NARROW>::kThreads, CtaShape<NARROW>::
   }
 }
 
+// What launch_umma launches for a problem on a GPU with `sms` multiprocessors; fills the tiling fields of `u`.
+struct UmmaLaunch {
+  bool narrow;
+  dim3 grid;
+  int threads;
+  size_t smem;
+};
+
+template <int MODE>
+UmmaLaunch shape_umma_launch(const DcnArgs &a, const UmmaPlan &p, int sms, UmmaArgs &u) {
+  using T = ModeTraits<MODE>;
+  u.tile_n = p.tile_n;
+  u.n_tiles = p.n_tiles;
+  u.k_blocks = p.k_blocks;
+  u.chan_blocks = p.chan_blocks;
+  u.m_tiles = p.m_tiles;
+  u.m_total = (int)p.m_total;
+  u.b_stage_bytes = (unsigned)p.b_stage_bytes;
+  // accumulator columns: tile_n, twice that with the cross-product accumulator; allocations are powers of two >= 32
+  const int slab = (p.tile_n + 31) / 32 * 32;
+  u.cross_col = slab;
+  const int set_cols = T::kParts * slab;      // one issuer's accumulators
+  // two issuers when the tile is narrow; each must always meet the same stages of both rings (even ring sizes)
+  static_assert(CtaShape<true>::kAStages % 2 == 0 && kBStages % 2 == 0, "two issuers need even rings");
+  u.dual = (p.tile_n <= 64 && p.k_blocks >= 2) ? 1 : 0;
+  u.acc2_col = set_cols;
+  int cols = 32;
+  while (cols < (u.dual ? 2 * set_cols : set_cols)) cols <<= 1;
+  u.tmem_cols = cols;
+  // every (kernel point, deformable group) pair a CTA's channels touch, if the table can hold them
+  const int cin_g_ = a.Cin / a.groups, cin_dg_ = a.Cin / a.dgroups;
+  // deformable groups the channels of one convolution group can span (groups and deformable groups need not nest)
+  int dg_per_cta = 1;
+  for (int g = 0; g < a.groups; ++g)
+    dg_per_cta = std::max(dg_per_cta, ((g + 1) * cin_g_ - 1) / cin_dg_ - (g * cin_g_) / cin_dg_ + 1);
+  const int wanted = a.Kh * a.Kw * dg_per_cta;
+  u.precomputed = wanted <= kMaxRecordSlots ? 1 : 0;
+  // Two CTAs per SM (CtaShape<true>; at most 256 TMEM columns each) when the tile is narrow and the grid is more
+  // than one wave of single CTAs; a grid that fits one wave is faster with the wide shape's four producer groups.
+  UmmaLaunch l;
+  l.narrow = p.tile_n <= 64 && (long long)p.m_tiles * p.n_tiles * a.groups > sms;
+  u.record_slots = u.precomputed ? wanted : (l.narrow ? CtaShape<true>::kGroups : kGroups);
+  l.smem = SmemLayout<MODE>::total(p.tile_n, u.record_slots, l.narrow ? CtaShape<true>::kAStages : kAStages);
+  l.grid = dim3(p.m_tiles, p.n_tiles, a.groups);
+  l.threads = l.narrow ? CtaShape<true>::kThreads : CtaShape<false>::kThreads;
+  return l;
+}
+
 template <int MODE>
 int launch_umma(const DcnArgs &a, const UmmaPlan &p, void *workspace, int32_t *status, cudaStream_t stream,
                 int reuse_flags = 0) {
@@ -1106,54 +1154,38 @@ int launch_umma(const DcnArgs &a, const UmmaPlan &p, void *workspace, int32_t *s
   u.xt = workspace;
   u.blob = blob;
   u.status = status;
-  u.tile_n = p.tile_n;
-  u.n_tiles = p.n_tiles;
-  u.k_blocks = p.k_blocks;
-  u.chan_blocks = p.chan_blocks;
-  u.m_tiles = p.m_tiles;
-  u.m_total = (int)p.m_total;
-  u.b_stage_bytes = (unsigned)p.b_stage_bytes;
-  // accumulator columns: tile_n, twice that with the cross-product accumulator; allocations are powers of two >= 32
-  const int slab = (p.tile_n + 31) / 32 * 32;
-  u.cross_col = slab;
-  const int set_cols = T::kParts * slab;      // one issuer's accumulators
-  // two issuers when the tile is narrow; each must always meet the same stages of both rings (even ring sizes)
-  static_assert(CtaShape<true>::kAStages % 2 == 0 && kBStages % 2 == 0, "two issuers need even rings");
-  u.dual = (p.tile_n <= 64 && p.k_blocks >= 2) ? 1 : 0;
-  u.acc2_col = set_cols;
-  int cols = 32;
-  while (cols < (u.dual ? 2 * set_cols : set_cols)) cols <<= 1;
-  u.tmem_cols = cols;
-  // every (kernel point, deformable group) pair a CTA's channels touch, if the table can hold them
-  const int cin_g_ = a.Cin / a.groups, cin_dg_ = a.Cin / a.dgroups;
-  // deformable groups the channels of one convolution group can span (groups and deformable groups need not nest)
-  int dg_per_cta = 1;
-  for (int g = 0; g < a.groups; ++g)
-    dg_per_cta = std::max(dg_per_cta, ((g + 1) * cin_g_ - 1) / cin_dg_ - (g * cin_g_) / cin_dg_ + 1);
-  const int wanted = a.Kh * a.Kw * dg_per_cta;
-  u.precomputed = wanted <= kMaxRecordSlots ? 1 : 0;
-  // Two CTAs per SM (CtaShape<true>; at most 256 TMEM columns each) when the tile is narrow and the grid is more
-  // than one wave of single CTAs; a grid that fits one wave is faster with the wide shape's four producer groups.
   int sms = 148, device = 0;
-  cudaGetDevice(&device);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-  const bool narrow = p.tile_n <= 64 && (long long)p.m_tiles * p.n_tiles * a.groups > sms;
-  u.record_slots = u.precomputed ? wanted : (narrow ? CtaShape<true>::kGroups : kGroups);
-  const size_t smem = SmemLayout<MODE>::total(p.tile_n, u.record_slots, narrow ? CtaShape<true>::kAStages : kAStages);
+  rc = check_cuda(cudaGetDevice(&device), "cudaGetDevice");
+  if (rc != GACB_OK) return rc;
+  rc = check_cuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device), "cudaDeviceGetAttribute(SM count)");
+  if (rc != GACB_OK) return rc;
+  if (device < 0 || device >= 64) return fail(GACB_ERR_UNSUPPORTED, "dcnv2: device ordinal %d is out of range", device);
+  const UmmaLaunch shape = shape_umma_launch<MODE>(a, p, sms, u);
+  const bool narrow = shape.narrow;
+  const size_t smem = shape.smem;
   const bool plain = a.offset == nullptr;
   auto kernel = narrow ? (plain ? dcn_umma_kernel<MODE, true, true> : dcn_umma_kernel<MODE, false, true>)
                        : (plain ? dcn_umma_kernel<MODE, true, false> : dcn_umma_kernel<MODE, false, false>);
-  rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                  "cudaFuncSetAttribute(dcn_umma_kernel)");
-  if (rc != GACB_OK) return rc;
-  if (narrow) {
-    // all of the unified array as shared memory, so that two CTAs fit
-    rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared),
-                    "cudaFuncSetAttribute(dcn_umma_kernel carve-out)");
-    if (rc != GACB_OK) return rc;
+  // Function attributes once per device and kernel variant (calls may come from several host threads): the largest
+  // shared-memory size any shape of this variant can ask for, and, for the narrow shape, all of the unified array
+  // as shared memory so that two CTAs fit.
+  static std::mutex attr_lock;
+  static bool attr_done[64][2][2] = {};
+  {
+    std::lock_guard<std::mutex> guard(attr_lock);
+    if (!attr_done[device][narrow][plain]) {
+      rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024),
+                      "cudaFuncSetAttribute(dcn_umma_kernel)");
+      if (rc != GACB_OK) return rc;
+      if (narrow) {
+        rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared),
+                        "cudaFuncSetAttribute(dcn_umma_kernel carve-out)");
+        if (rc != GACB_OK) return rc;
+      }
+      attr_done[device][narrow][plain] = true;
+    }
   }
-  dim3 grid(p.m_tiles, p.n_tiles, a.groups);
-  kernel<<<grid, narrow ? CtaShape<true>::kThreads : CtaShape<false>::kThreads, smem, stream>>>(u);
+  kernel<<<shape.grid, shape.threads, smem, stream>>>(u);
   return check_cuda(cudaGetLastError(), "dcn_umma_kernel launch");
 }
 
@@ -1438,4 +1470,47 @@ GACB_API int gacb_dcnv2_forward_static(const float *x, const float *offset, cons
     case MODE_TF32: return launch_umma<MODE_TF32>(a, p, scratch, status_word, stream);
     default: return launch_umma<MODE_F32X3>(a, p, scratch, status_word, stream);
   }
+}
+
+GACB_API int gacb_dcnv2_launch_geometry(int n, int Cin, int H, int W, int Cout, int Kh, int Kw, int sh, int sw, int ph,
+                                        int pw, int dh, int dw, int groups, int deform_groups, int math_mode, int plain,
+                                        int sm_count, gacb_launch_geometry *out) {
+  if (!out) return fail(GACB_ERR_INVALID_ARGUMENT, "launch_geometry: out is NULL");
+  DcnArgs a{};
+  math_mode &= 0xff;
+  int rc = validate(a, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, n, Cin, H, W, Cout, Kh, Kw, sh, sw, ph, pw, dh,
+                    dw, groups, deform_groups, 0, 0, math_mode, -1, -1, plain != 0);
+  if (rc != GACB_OK) return rc;
+  a.n_begin = 0;
+  a.n_end = n;
+  a.m_count = n * a.Ho * a.Wo;
+  // only the launch shape is wanted: stand-ins keep "is this a plain convolution" readable from the operands
+  static const float kDummy = 0.0f;
+  a.offset = plain ? nullptr : &kDummy;
+  *out = gacb_launch_geometry{};
+  UmmaPlan p;
+  if (n <= 0 || !plan_umma(a, math_mode, p)) {
+    const long long total = (long long)Cout * a.m_count;
+    out->grid[0] = (int)((total + 255) / 256); out->grid[1] = out->grid[2] = 1;
+    out->block[0] = 256; out->block[1] = out->block[2] = 1;
+    out->units_per_cta = 256;
+    snprintf(out->kernel, sizeof(out->kernel), "dcn_direct_kernel");
+    return GACB_OK;
+  }
+  UmmaArgs u{};
+  UmmaLaunch l;
+  if (sm_count <= 0) sm_count = 148;
+  switch (math_mode) {
+    case MODE_BF16: l = shape_umma_launch<MODE_BF16>(a, p, sm_count, u); break;
+    case MODE_TF32: l = shape_umma_launch<MODE_TF32>(a, p, sm_count, u); break;
+    default: l = shape_umma_launch<MODE_F32X3>(a, p, sm_count, u); break;
+  }
+  out->grid[0] = (int)l.grid.x; out->grid[1] = (int)l.grid.y; out->grid[2] = (int)l.grid.z;
+  out->block[0] = l.threads; out->block[1] = out->block[2] = 1;
+  out->dynamic_smem_bytes = l.smem;
+  out->units_per_cta = kTileM;
+  snprintf(out->kernel, sizeof(out->kernel), "dcn_umma_kernel<%s,%s,%s>",
+           math_mode == MODE_BF16 ? "bf16" : (math_mode == MODE_TF32 ? "tf32" : "f32x3"), plain ? "plain" : "deform",
+           l.narrow ? "narrow" : "wide");
+  return GACB_OK;
 }

@@ -60,6 +60,9 @@ constexpr int kMaxCoordRank = 8;
 #ifndef GACB_MSDA_UNROLL
 #define GACB_MSDA_UNROLL 4
 #endif
+#ifndef GACB_MSDA_FFMA2
+#define GACB_MSDA_FFMA2 0
+#endif
 constexpr int kRecordsPerThread = GACB_MSDA_RECORDS_PER_THREAD;   // phase-A budget: 20-byte tap records per thread of the CTA
 constexpr int kMaxRowsPerGroup = 8;
 constexpr int kCarveoutPercent = GACB_MSDA_CARVEOUT;  // shared-memory share of the 256 KB; the rest is L1
@@ -305,10 +308,18 @@ struct Tap<float, 4> {
   // Compiler fence on a loaded value: everything that uses it is scheduled after every load that precedes the fence.
   __device__ static __forceinline__ void pin(Raw &v) { asm volatile("" : "+f"(v.x), "+f"(v.y), "+f"(v.z), "+f"(v.w)); }
   __device__ static __forceinline__ void fma(float (&acc)[4], const Raw &v, float c) {
+#if GACB_MSDA_FFMA2
+    // two float32 FMAs per instruction (sm_100 FFMA2): each half is the same correctly rounded fmaf
+    const float2 cc = make_float2(c, c);
+    const float2 lo = __ffma2_rn(make_float2(v.x, v.y), cc, make_float2(acc[0], acc[1]));
+    const float2 hi = __ffma2_rn(make_float2(v.z, v.w), cc, make_float2(acc[2], acc[3]));
+    acc[0] = lo.x; acc[1] = lo.y; acc[2] = hi.x; acc[3] = hi.y;
+#else
     acc[0] = fmaf(v.x, c, acc[0]);
     acc[1] = fmaf(v.y, c, acc[1]);
     acc[2] = fmaf(v.z, c, acc[2]);
     acc[3] = fmaf(v.w, c, acc[3]);
+#endif
   }
 };
 
@@ -320,6 +331,17 @@ struct Tap<__nv_bfloat16, 8> {
   }
   __device__ static __forceinline__ void pin(Raw &v) { asm volatile("" : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)); }
   __device__ static __forceinline__ void fma(float (&acc)[8], const Raw &v, float c) {
+#if GACB_MSDA_FFMA2
+    const float2 cc = make_float2(c, c);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 r = __ffma2_rn(make_float2(bf16_lo(w[k]), bf16_hi(w[k])), cc, make_float2(acc[2 * k], acc[2 * k + 1]));
+      acc[2 * k] = r.x;
+      acc[2 * k + 1] = r.y;
+    }
+    return;
+#endif
     acc[0] = fmaf(bf16_lo(v.x), c, acc[0]);
     acc[1] = fmaf(bf16_hi(v.x), c, acc[1]);
     acc[2] = fmaf(bf16_lo(v.y), c, acc[2]);
@@ -1263,3 +1285,62 @@ GACB_API int gacb_msda_tile_path(int mode) {
   return previous;
 }
 
+
+namespace {
+template <typename VT>
+bool rows_geometry(MsdaArgs &a, int cpl, gacb_launch_geometry *out) {
+  RowsGeometry g;
+  switch (a.D / cpl) {
+    case 1: g = plan_rows<VT, 1>(a); break;
+    case 2: g = plan_rows<VT, 2>(a); break;
+    case 4: g = plan_rows<VT, 4>(a); break;
+    case 8: g = plan_rows<VT, 8>(a); break;
+    case 16: g = plan_rows<VT, 16>(a); break;
+    case 32: g = plan_rows<VT, 32>(a); break;
+    default: return false;
+  }
+  out->grid[0] = g.grid; out->grid[1] = out->grid[2] = 1;
+  out->block[0] = g.threads; out->block[1] = out->block[2] = 1;
+  out->dynamic_smem_bytes = g.smem;
+  out->units_per_cta = g.rows_per_cta;
+  return true;
+}
+}  // namespace
+
+GACB_API int gacb_msda_launch_geometry(int value_dtype, const int32_t *spatial_hw, int L, int B, int S, int Q, int H, int D,
+                                       int P, int q_begin, int q_end, gacb_launch_geometry *out) {
+  if (!out) return fail(GACB_ERR_INVALID_ARGUMENT, "launch_geometry: out is NULL");
+  MsdaArgs a{};
+  static const float kDummy = 0.0f;     // never dereferenced: only the launch shape is wanted
+  float sink = 0.0f;
+  int rc = fill_common(a, &kDummy, value_dtype, &kDummy, &kDummy, &sink, spatial_hw, L, B, S, Q, H, D, P, q_begin, q_end);
+  if (rc != GACB_OK) return rc;
+  *out = gacb_launch_geometry{};
+  if (a.total_rows == 0) {
+    snprintf(out->kernel, sizeof(out->kernel), "none");
+    return GACB_OK;
+  }
+  if (tile_path_applies(a, value_dtype)) {
+    const TileGeometry g = plan_tile(a);
+    out->grid[0] = (int)g.grid.x; out->grid[1] = (int)g.grid.y; out->grid[2] = (int)g.grid.z;
+    out->block[0] = g.threads; out->block[1] = out->block[2] = 1;
+    out->dynamic_smem_bytes = g.smem;
+    out->units_per_cta = kTileRows;
+    snprintf(out->kernel, sizeof(out->kernel), "msda_tile_kernel<%d>", a.chunk_pad);
+    return GACB_OK;
+  }
+  bool vector = false;
+  if (value_dtype == GACB_F32 && D % 4 == 0) vector = rows_geometry<float>(a, 4, out);
+  if (value_dtype == GACB_BF16 && D % 8 == 0) vector = rows_geometry<__nv_bfloat16>(a, 8, out);
+  if (vector) {
+    snprintf(out->kernel, sizeof(out->kernel), "msda_rows_kernel<%s,%d,%d>", value_dtype == GACB_F32 ? "float" : "bf16",
+             value_dtype == GACB_F32 ? 4 : 8, D / (value_dtype == GACB_F32 ? 4 : 8));
+    return GACB_OK;
+  }
+  const long long elems = (long long)a.total_rows * a.D;
+  out->grid[0] = (int)((elems + kThreads - 1) / kThreads); out->grid[1] = out->grid[2] = 1;
+  out->block[0] = kThreads; out->block[1] = out->block[2] = 1;
+  out->units_per_cta = kThreads;
+  snprintf(out->kernel, sizeof(out->kernel), "msda_generic_kernel");
+  return GACB_OK;
+}

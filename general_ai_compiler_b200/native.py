@@ -56,6 +56,13 @@ class MsdaDesc(ctypes.Structure):
     ]
 
 
+class LaunchGeometry(ctypes.Structure):
+    """``gacb_launch_geometry`` of include/gacb.h."""
+
+    _fields_ = [("grid", _i * 3), ("block", _i * 3), ("dynamic_smem_bytes", _sz), ("units_per_cta", _i),
+                ("kernel", ctypes.c_char * 64)]
+
+
 # name -> (restype, argtypes); must list every symbol include/gacb.h declares.
 SIGNATURES = {
     "gacb_version": (_i, []),
@@ -77,6 +84,8 @@ SIGNATURES = {
                                  + [_i] * 18 + [_vp, _sz, _vp, _vp]),
     "gacb_dcnv2_workspace_bytes": (_sz, [_i] * 16),
     "gacb_dcnv2_forward_static": (_i, [_vp] * 6 + [_i] * 18 + [_vp, _vp]),
+    "gacb_msda_launch_geometry": (_i, [_i, _ip] + [_i] * 9 + [ctypes.POINTER(LaunchGeometry)]),
+    "gacb_dcnv2_launch_geometry": (_i, [_i] * 18 + [ctypes.POINTER(LaunchGeometry)]),
     "gacb_status_from_word": (_i, [ctypes.c_int32]),
     "gacb_read_status_word": (_i, [_vp, _vp]),
     "gacb_cast_f32_to_bf16": (_i, [_vp, _vp, _sz, _vp]),
@@ -131,3 +140,24 @@ def check(status: int, what: str) -> None:
 def int32_table(values) -> ctypes.Array:
     flat = [int(v) for v in values]
     return (ctypes.c_int32 * len(flat))(*flat)
+
+
+def msda_launch_geometry(value_dtype: int, spatial_shapes, B: int, Q: int, H: int, D: int, P: int,
+                         q_range=None) -> LaunchGeometry:
+    shapes = [(int(h), int(w)) for h, w in spatial_shapes]
+    geo = LaunchGeometry()
+    q0, q1 = (0, Q) if q_range is None else q_range
+    rc = load().gacb_msda_launch_geometry(value_dtype, int32_table(v for pair in shapes for v in pair), len(shapes), B,
+                                          sum(h * w for h, w in shapes), Q, H, D, P, q0, q1, ctypes.byref(geo))
+    check(rc, "gacb_msda_launch_geometry")
+    return geo
+
+
+def dcnv2_launch_geometry(n, Cin, H, W, Cout, Kh, Kw, stride, padding, dilation, groups, deform_groups, math_mode: int,
+                          plain: bool = False, sm_count: int = 0) -> LaunchGeometry:
+    geo = LaunchGeometry()
+    rc = load().gacb_dcnv2_launch_geometry(n, Cin, H, W, Cout, Kh, Kw, stride[0], stride[1], padding[0], padding[1],
+                                           dilation[0], dilation[1], groups, deform_groups, math_mode, 1 if plain else 0,
+                                           sm_count, ctypes.byref(geo))
+    check(rc, "gacb_dcnv2_launch_geometry")
+    return geo

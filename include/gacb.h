@@ -289,6 +289,26 @@ int gacb_dcnv2_forward_static(const float *x, const float *offset, const float *
                               int deform_groups, int n_begin, int n_end, int math_mode,
                               int32_t *status_word, void *stream);
 
+/* The launch the library makes for a problem, without making it: which kernel, grid, block, dynamic shared memory
+ * and how many work units (MSDA: (batch, query, head) rows; convolutions: output pixels) one thread block covers.
+ * Pure host functions (no CUDA call, no device needed).  They replace the launch metadata GAC's compiler attaches to
+ * its generated kernels (`KernelLaunch.grid/block`, src/gac/targets/cuda/compiler.py:40-55; `grid_size`, `block_size`
+ * of a plan.json dispatch, native/lib/DeviceLowering.cpp:1641-1656): here the kernels are precompiled, so the
+ * library is the one place that knows their shapes.  `sm_count` (<= 0: 148) matters because convolutions with
+ * narrow channel tiles switch to a two-CTAs-per-SM shape when the grid exceeds one wave.  The MSDA answer is for
+ * the plain entry points (no visibility, no fused coordinates) under the current gacb_msda_tile_path mode. */
+typedef struct gacb_launch_geometry {
+  int grid[3], block[3];
+  size_t dynamic_smem_bytes;
+  int units_per_cta;
+  char kernel[64];
+} gacb_launch_geometry;
+int gacb_msda_launch_geometry(int value_dtype, const int32_t *spatial_hw, int L, int B, int S, int Q, int H, int D,
+                              int P, int q_begin, int q_end, gacb_launch_geometry *out);
+int gacb_dcnv2_launch_geometry(int n, int Cin, int H, int W, int Cout, int Kh, int Kw, int sh, int sw, int ph, int pw,
+                               int dh, int dw, int groups, int deform_groups, int math_mode, int plain, int sm_count,
+                               gacb_launch_geometry *out);
+
 /* The device status word of the calls above, turned into a status.  (GAC reports a failed device step as a
  * `failed` session / a `status:"failed"` report with the failing stage: src/gac/execution/cuda.py:457-464,
  * native/runtime/cuda-run.cpp:685-703.)

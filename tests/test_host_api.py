@@ -179,14 +179,41 @@ def test_compile_plans_one_launch_per_node():
     assert len(first.launches) == 1
     launch = first.launches[0]
     assert launch.node_id == "msda" and launch.entry_point == "gacb_msda_forward"
-    assert launch.block == (256, 1, 1)
-    # 6*2500*8 rows, 8 samples each: 32 rows side by side x 2 row batches per CTA
-    assert msda_rows_per_cta(32, 8) == 64 and launch.grid == (1875, 1, 1)
+    # the launch metadata is what the library launches (gacb_msda_launch_geometry): float32 texels run thread
+    # blocks of 128 threads, 16 rows side by side; 6*2500*8 rows with 8 samples each take two row batches per block
+    assert launch.block == (128, 1, 1) and launch.implementation_candidates == ("msda_rows_kernel<float,4,8>",)
+    assert msda_rows_per_cta(32, 8) == 32 and launch.grid == (6 * 2500 * 8 // 32, 1, 1)
+    assert msda_rows_per_cta(32, 8, "bfloat16") == 64 and msda_rows_per_cta(6, 8) is None
     assert first.describe()["tensor_bytes_upper_bound"] == 29_184_000
     base = compile_cuda(build_msda_graph_for(WORKLOADS["base_sca"]))
-    assert base.launches[0].grid == (15000, 1, 1)
+    assert base.launches[0].grid == (30000, 1, 1) and base.launches[0].block == (128, 1, 1)
+    bf16 = compile_cuda(build_msda_graph_for(WORKLOADS["base_sca"]), value_storage="bfloat16")
+    assert bf16.launches[0].grid == (7500, 1, 1) and bf16.launches[0].block == (256, 1, 1)
     dcn = compile_cuda(build_dcn_graph_for(WORKLOADS["dcn_c4"]), dcn_math="bf16")
     assert dcn.launches[0].entry_point == "gacb_dcnv2_forward" and dcn.options["dcn_math"] == "bf16"
+    # 6 * 58 * 100 output pixels in tiles of 128, one 256-channel tile, 19 warps per thread block
+    assert dcn.launches[0].grid == (272, 1, 1) and dcn.launches[0].block == (608, 1, 1)
+    assert dcn.launches[0].implementation_candidates == ("dcn_umma_kernel<bf16,deform,wide>",)
+    assert "3xTF32" not in first.describe()["precision"]
+
+
+def test_launch_geometry_follows_the_kernel_dispatch_rules():
+    """What compile_cuda reports is computed by the same planning code that launches: spot checks of its rules."""
+    from general_ai_compiler_b200 import native
+
+    tiny = native.dcnv2_launch_geometry(1, 8, 5, 5, 8, 3, 3, (1, 1), (1, 1), (1, 1), 1, 1, native.DCN_BF16)
+    assert tiny.kernel == b"dcn_direct_kernel" and tuple(tiny.block) == (256, 1, 1) and tuple(tiny.grid) == (1, 1, 1)
+    conv = native.dcnv2_launch_geometry(6, 256, 58, 100, 27, 3, 3, (1, 1), (1, 1), (1, 1), 1, 1, native.DCN_BF16, plain=True)
+    assert conv.kernel == b"dcn_umma_kernel<bf16,plain,narrow>" and tuple(conv.block) == (352, 1, 1)
+    one_wave = native.dcnv2_launch_geometry(3, 256, 58, 100, 27, 3, 3, (1, 1), (1, 1), (1, 1), 1, 1, native.DCN_BF16, plain=True)
+    assert one_wave.kernel == b"dcn_umma_kernel<bf16,plain,wide>" and tuple(one_wave.grid) == (136, 1, 1)
+    c5 = native.dcnv2_launch_geometry(6, 512, 29, 50, 512, 3, 3, (1, 1), (1, 1), (1, 1), 1, 1, native.DCN_F32X3)
+    assert tuple(c5.grid) == (68, 2, 1) and c5.dynamic_smem_bytes <= 227 * 1024
+    odd = native.msda_launch_geometry(native.GACB_F32, [(3, 5)], 2, 7, 3, 6, 2)
+    assert odd.kernel == b"msda_generic_kernel" and tuple(odd.block) == (256, 1, 1) and odd.grid[0] == 1
+    part = native.msda_launch_geometry(native.GACB_F32, [(116, 200), (58, 100), (29, 50), (15, 25)], 6, 10000, 8, 32, 8,
+                                       q_range=(1250, 2500))
+    assert part.grid[0] == 6 * 1250 * 8 // 16 and part.units_per_cta == 16
 
 
 def test_backend_rejects_non_float32_and_unknown_ops():
