@@ -95,6 +95,29 @@ def _build_variant(extra_flags: tuple, output: Path, verbose: bool) -> Path:
     return output
 
 
+# Test builds of the same sources, kept beside the library (git-ignored, they travel with the tree):
+#   libgacb_checked.so      every kernel index range-checked (gacb_checked_violations)
+#   libgacb_faultinject.so  short bounded-wait limit and a flag that makes the DCNv2 weight loader skip its copies,
+#                           so that a wait runs out and the kernel leaves through its abort path
+VARIANTS = {
+    "libgacb_checked.so": ("-DGACB_CHECKED=1",),
+    "libgacb_faultinject.so": ("-DGACB_DCN_FAULT_INJECT=1", "-DGACB_DCN_SPIN_LIMIT=4096"),
+}
+
+
+def build_variants(force: bool = False, verbose: bool = False) -> list[Path]:
+    """Build the test variants whose file is missing or older than a source; returns their paths."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + [PKG_DIR.parent / "include" / "gacb.h"]
+    newest = max(p.stat().st_mtime for p in deps)
+    todo = [(name, flags) for name, flags in VARIANTS.items()
+            if force or not (PKG_DIR / name).exists() or (PKG_DIR / name).stat().st_mtime < newest]
+    with ThreadPoolExecutor(max_workers=max(1, len(todo))) as pool:
+        list(pool.map(lambda nf: _build_variant(nf[1], PKG_DIR / nf[0], verbose), todo))
+    return [PKG_DIR / name for name in VARIANTS]
+
+
 RUNNER_SRC = CSRC / "runner" / "gacb_run.cpp"
 RUNNER_PATH = PKG_DIR / "gacb-run"
 

@@ -58,6 +58,10 @@
 namespace gacb {
 namespace {
 
+GACB_CHECK_RECORD;
+// Sites of the checked build in this file: 11 tap-record table, 12 gathers from the channel-last copy,
+// 13 offset / mask operands, 14 output elements, 15 packed-weight stages.
+
 // Scratch of gacb_dcnv2_forward_static: lives in the module's global memory on every GPU that loads the library,
 // from load until the process exits.  Host code must not pass this name to a kernel (on the host it is only a
 // stand-in for the symbol); the device address comes from cudaGetSymbolAddress, once per device.
@@ -235,7 +239,18 @@ struct CtaShape {
   static constexpr int kMinCtas = NARROW ? 2 : 1;
 };
 constexpr double kMinTensorFlopsPerImage = 12e6;
-constexpr uint32_t kSpinLimit = 1u << 22;        // bounded mbarrier polling (each poll may block ~us in hardware)
+// Bounded mbarrier polling (each poll may block ~us in hardware).  GACB_DCN_SPIN_LIMIT shortens it in the test
+// build that makes a wait run out on purpose (GACB_DCN_FAULT_INJECT, see UmmaArgs::drop_weight_copies).
+#ifndef GACB_DCN_SPIN_LIMIT
+#define GACB_DCN_SPIN_LIMIT (1u << 22)
+#endif
+#ifndef GACB_DCN_FAULT_INJECT
+#define GACB_DCN_FAULT_INJECT 0
+#endif
+constexpr uint32_t kSpinLimit = GACB_DCN_SPIN_LIMIT;
+// math_mode flag of the test build only: the weight loader issues none of its copies, so the tensor-core thread's
+// wait for the first weight stage runs out and the kernel has to unwind through its abort path.
+constexpr int kTestDropWeightCopies = 0x400;
 
 enum { MODE_F32X3 = GACB_DCN_F32X3, MODE_TF32 = GACB_DCN_TF32, MODE_BF16 = GACB_DCN_BF16 };
 
@@ -540,6 +555,7 @@ struct UmmaArgs {
   int record_slots;            // slots of the tap-record table
   int precomputed;             // the table holds every (kernel point, deformable group) record of a tile
   unsigned b_stage_bytes;
+  int drop_weight_copies;      // test build only (GACB_DCN_FAULT_INJECT): the loader skips every copy
 };
 
 // Tap records live in shared memory as two arrays of record_slots x 128 entries: a packed geometry word and the
@@ -721,10 +737,12 @@ __global__ void __launch_bounds__(CtaShape<NARROW>::kThreads, CtaShape<NARROW>::
         if constexpr (!PLAIN) {
           const int n = a.n_begin + t.img;
           const int mch = dgi * K + kp;
-          const float *off = a.offset + ((long long)n * 2 * a.dgroups * K + 2 * mch) * plane_out + t.pix;
+          const long long mask_elems = (long long)a.N * a.dgroups * K * plane_out;
+          const float *off = a.offset + GACB_INDEX(((long long)n * 2 * a.dgroups * K + 2 * mch) * plane_out + t.pix,
+                                                   2 * mask_elems - plane_out, 13);
           t.dy = __ldg(off);
           t.dx = __ldg(off + plane_out);
-          t.mk = __ldg(a.mask + ((long long)n * a.dgroups * K + mch) * plane_out + t.pix);
+          t.mk = __ldg(a.mask + GACB_INDEX(((long long)n * a.dgroups * K + mch) * plane_out + t.pix, mask_elems, 13));
         }
       }
       return t;
@@ -764,12 +782,12 @@ __global__ void __launch_bounds__(CtaShape<NARROW>::kThreads, CtaShape<NARROW>::
       if constexpr (MODE == MODE_BF16) {
         // BF16 mode blends in bf16x2, so its record carries the coefficients already rounded to bf16 and is one
         // 16-byte word: {geometry, c0 | c1 << 16, c2 | c3 << 16, unused} -- one shared-memory read per item
-        reinterpret_cast<uint4 *>(rec_cf)[slot * kTileM + row] =
+        reinterpret_cast<uint4 *>(rec_cf)[GACB_INDEX(slot * kTileM + row, u.record_slots * kTileM, 11)] =
             make_uint4(geo, pack_bf16x2(__float2bfloat16_rn(cf.x), __float2bfloat16_rn(cf.y)),
                        pack_bf16x2(__float2bfloat16_rn(cf.z), __float2bfloat16_rn(cf.w)), 0u);
       } else {
-        rec_geo[slot * kTileM + row] = geo;
-        rec_cf[slot * kTileM + row] = cf;
+        rec_geo[GACB_INDEX(slot * kTileM + row, u.record_slots * kTileM, 11)] = geo;
+        rec_cf[GACB_INDEX(slot * kTileM + row, u.record_slots * kTileM, 11)] = cf;
       }
     };
     // group-only barrier (ids 1..4), 128 threads
@@ -825,8 +843,8 @@ __global__ void __launch_bounds__(CtaShape<NARROW>::kThreads, CtaShape<NARROW>::
         finish_record(g, gt, kp, fetch_raw(gt, kp, dgi_of(cb)));
         group_sync();                                         // this block's records are complete
       }
-      const uint32_t *geo_row = rec_geo + slot * kTileM;
-      const float4 *cf_row = rec_cf + slot * kTileM;
+      const uint32_t *geo_row = rec_geo + GACB_INDEX(slot, u.record_slots, 11) * kTileM;
+      const float4 *cf_row = rec_cf + GACB_INDEX(slot, u.record_slots, 11) * kTileM;
       if (alive) alive = mbar_wait(empty_a(sa), ((kb / SA) & 1) ^ 1, abort_flag);
       if (alive) {
         unsigned char *a_hi = a_stages + sa * a_stage;
@@ -849,12 +867,15 @@ __global__ void __launch_bounds__(CtaShape<NARROW>::kThreads, CtaShape<NARROW>::
               cf[b] = cf_row[row];
             }
             const int e = lane_elem + (int)(geo & ~3u);
-            v[b][0] = Quad::load(xt, e);
+#if GACB_CHECKED
+            const long long xt_last = (long long)(a.n_end - a.n_begin) * image_elems - kChanPerLane + 1;
+#endif
+            v[b][0] = Quad::load(xt, GACB_INDEX(e, xt_last, 12));
             if constexpr (!PLAIN) {
               const int sx = (geo & 1u) ? step_x : 0, sy = (geo & 2u) ? step_y : 0;
-              v[b][1] = Quad::load(xt, e + sx);
-              v[b][2] = Quad::load(xt, e + sy);
-              v[b][3] = Quad::load(xt, e + sy + sx);
+              v[b][1] = Quad::load(xt, GACB_INDEX(e + sx, xt_last, 12));
+              v[b][2] = Quad::load(xt, GACB_INDEX(e + sy, xt_last, 12));
+              v[b][3] = Quad::load(xt, GACB_INDEX(e + sy + sx, xt_last, 12));
             }
           }
 #pragma unroll
@@ -993,6 +1014,12 @@ __global__ void __launch_bounds__(CtaShape<NARROW>::kThreads, CtaShape<NARROW>::
             if (col + j < cols) {
               const int co = co0 + j;
               float *dst = (co < split_at ? y_lo : y_hi) + (long long)co * plane_out;
+#if GACB_CHECKED
+              // the element must lie inside the tensor it goes to: y [N, split_at, plane] or y_split [N, Cout - split_at, plane]
+              const long long rel = co < split_at ? dst - a.y : dst - a.y_split;
+              const long long lim = (long long)a.N * (co < split_at ? split_at : a.Cout - split_at) * plane_out;
+              if (GACB_INDEX(rel, lim, 14) != rel) continue;
+#endif
               __stcs(dst, __uint_as_float(r[j]));
             }
           }
@@ -1009,8 +1036,9 @@ __global__ void __launch_bounds__(CtaShape<NARROW>::kThreads, CtaShape<NARROW>::
       for (int kb = 0; kb < k_blocks; ++kb) {
         const int s = kb % SB;
         if (!mbar_wait(empty_b(s), ((kb / SB) & 1) ^ 1, abort_flag)) break;
+        if (GACB_DCN_FAULT_INJECT && u.drop_weight_copies) continue;   // nothing issued: nothing to drain later
         mbar_arrive_expect_tx(full_b(s), b_bytes);
-        bulk_copy_g2s(smem_u32(b_stages + s * b_stage), src + (size_t)kb * b_bytes, b_bytes, full_b(s));
+        bulk_copy_g2s(smem_u32(b_stages + s * b_stage), src + (size_t)GACB_INDEX(kb, k_blocks, 15) * b_bytes, b_bytes, full_b(s));
         issued = kb + 1;
       }
       if (*abort_flag) {
@@ -1154,6 +1182,7 @@ int launch_umma(const DcnArgs &a, const UmmaPlan &p, void *workspace, int32_t *s
   u.xt = workspace;
   u.blob = blob;
   u.status = status;
+  u.drop_weight_copies = (reuse_flags & kTestDropWeightCopies) ? 1 : 0;
   int sms = 148, device = 0;
   rc = check_cuda(cudaGetDevice(&device), "cudaGetDevice");
   if (rc != GACB_OK) return rc;
@@ -1271,7 +1300,7 @@ static int dcnv2_forward_impl(const float *x, const float *offset, const float *
   DcnArgs a{};
   const int reuse_flags = math_mode & ~0xff;
   math_mode &= 0xff;
-  if (reuse_flags & ~(GACB_DCN_REUSE_WEIGHTS | GACB_DCN_REUSE_INPUT))
+  if (reuse_flags & ~(GACB_DCN_REUSE_WEIGHTS | GACB_DCN_REUSE_INPUT | (GACB_DCN_FAULT_INJECT ? kTestDropWeightCopies : 0)))
     return fail(GACB_ERR_INVALID_ARGUMENT, "dcnv2: unknown flag bits 0x%x in math_mode", reuse_flags);
   int rc = validate(a, x, offset, mask, w, bias, y, N, Cin, H, W, Cout, Kh, Kw, sh, sw, ph, pw, dh, dw, groups,
                     deform_groups, n_begin, n_end, math_mode, extras.pad_bottom, extras.pad_right, extras.plain);
@@ -1471,6 +1500,17 @@ GACB_API int gacb_dcnv2_forward_static(const float *x, const float *offset, cons
     default: return launch_umma<MODE_F32X3>(a, p, scratch, status_word, stream);
   }
 }
+
+namespace gacb {
+int dcn_check_record(unsigned int out[2]) {
+  out[0] = out[1] = 0;
+#if GACB_CHECKED
+  return check_cuda(cudaMemcpyFromSymbol(out, g_check_record, 2 * sizeof(unsigned int)), "cudaMemcpyFromSymbol(check record)");
+#else
+  return GACB_OK;
+#endif
+}
+}  // namespace gacb
 
 GACB_API int gacb_dcnv2_launch_geometry(int n, int Cin, int H, int W, int Cout, int Kh, int Kw, int sh, int sw, int ph,
                                         int pw, int dh, int dw, int groups, int deform_groups, int math_mode, int plain,

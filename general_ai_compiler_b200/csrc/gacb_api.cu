@@ -64,3 +64,19 @@ GACB_API int gacb_read_status_word(const int32_t *status_word, void *stream) {
   if (e != cudaSuccess) return gacb::check_cuda(e, "read_status_word");
   return gacb_status_from_word(word);
 }
+
+GACB_API int gacb_checked_violations(unsigned int *count, unsigned int *last_site) {
+#if GACB_CHECKED
+  unsigned int m[2] = {0, 0}, d[2] = {0, 0};
+  int rc = gacb::msda_check_record(m);
+  if (rc == GACB_OK) rc = gacb::dcn_check_record(d);
+  if (rc != GACB_OK) return rc;
+  if (count) *count = m[0] + d[0];
+  if (last_site) *last_site = d[0] ? d[1] : m[1];
+  return GACB_OK;
+#else
+  (void)count;
+  (void)last_site;
+  return gacb::fail(GACB_ERR_UNSUPPORTED, "this libgacb.so was not built with -DGACB_CHECKED=1");
+#endif
+}

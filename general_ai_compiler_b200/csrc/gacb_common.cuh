@@ -46,6 +46,31 @@ __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w 
 __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 
 
+// Checked build (-DGACB_CHECKED=1): the stand-in for a memory checker on boxes where none can be run.  Every
+// gather offset, record-table slot and output index of the kernels goes through GACB_INDEX(index, limit, site):
+// an index outside [0, limit) is counted in the translation unit's violation record (count, last site) and
+// replaced by 0, so the access is skipped in effect and nothing faults.  gacb_checked_violations() reads the
+// records.  In the normal build the macro is the index itself.
+#ifndef GACB_CHECKED
+#define GACB_CHECKED 0
+#endif
+#if GACB_CHECKED
+#define GACB_CHECK_RECORD static __device__ unsigned int g_check_record[2]
+#define GACB_INDEX(index, limit, site) gacb::checked_index((long long)(index), (long long)(limit), (site), g_check_record)
+__device__ __forceinline__ long long checked_index(long long index, long long limit, unsigned int site, unsigned int *record) {
+  if (index >= 0 && index < limit) return index;
+  atomicAdd(&record[0], 1u);
+  record[1] = site;
+  return 0;
+}
+#else
+#define GACB_CHECK_RECORD static_assert(true, "")
+#define GACB_INDEX(index, limit, site) (index)
+#endif
+// Per translation unit: (violations, last site) of the checked build; both 0 in the normal build.
+int msda_check_record(unsigned int out[2]);
+int dcn_check_record(unsigned int out[2]);
+
 // mbarrier and bulk-copy wrappers (sm_90+ PTX) shared by the kernels that stage tiles in shared memory.
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

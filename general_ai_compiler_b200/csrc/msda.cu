@@ -38,6 +38,15 @@
 namespace gacb {
 namespace {
 
+GACB_CHECK_RECORD;
+// Sites of the checked build in this file: 1 row table, 2 tap-record table, 3 locations / weights / scores,
+// 4 value taps, 5 output rows, 6 compacted row list, 7 normalizer / reference of the fused form.
+#if GACB_CHECKED
+#define GACB_TAP(o) ((int)(GACB_INDEX((long long)base_off + (o), value_elems - CPL + 1, 4) - base_off))
+#else
+#define GACB_TAP(o) (o)
+#endif
+
 constexpr int kThreads = 256;
 constexpr int kMaxLevels = 32;
 constexpr int kMaxPoints = 64;
@@ -116,6 +125,7 @@ struct MsdaArgs {
   FastDiv coord_div[kMaxCoordRank];
   int comp_split;                 // the (x, y) axis is handled apart: index with the sample number, not the element
   int ref_comp_stride;
+  long long norm_elems, ref_elems;   // element counts of normalizer / reference (bounds of the checked build)
 };
 
 struct __align__(16) TapEntry {
@@ -165,10 +175,10 @@ __device__ __forceinline__ float2 fused_coordinates(const MsdaArgs &a, const Row
     rx = reference_index(a, 2u * (uint32_t)si);
     ry = reference_index(a, 2u * (uint32_t)si + 1u);
   }
-  const float2 off = ld_stream_f2(a.loc + 2 * si);
-  const float qx = __fdiv_rn(off.x, a.normalizer[ni]);
-  const float qy = __fdiv_rn(off.y, a.normalizer[ni + a.norm_stride[5]]);
-  const float bx = a.reference[rx], by = a.reference[ry];
+  const float2 off = ld_stream_f2(a.loc + 2 * GACB_INDEX(si, (long long)a.B * a.Q * a.H * a.LP, 3));
+  const float qx = __fdiv_rn(off.x, a.normalizer[GACB_INDEX(ni, a.norm_elems, 7)]);
+  const float qy = __fdiv_rn(off.y, a.normalizer[GACB_INDEX(ni + a.norm_stride[5], a.norm_elems, 7)]);
+  const float bx = a.reference[GACB_INDEX(rx, a.ref_elems, 7)], by = a.reference[GACB_INDEX(ry, a.ref_elems, 7)];
   return a.reference_first ? make_float2(__fadd_rn(bx, qx), __fadd_rn(by, qy))
                            : make_float2(__fadd_rn(qx, bx), __fadd_rn(qy, by));
 }
@@ -206,11 +216,11 @@ __device__ __forceinline__ SampleGeom sample_geometry(const MsdaArgs &a, int gro
     lx = v.x;
     ly = v.y;
   } else {
-    const float2 v = ld_stream_f2(a.loc + 2 * si);
+    const float2 v = ld_stream_f2(a.loc + 2 * GACB_INDEX(si, (long long)a.B * a.Q * a.H * a.LP, 3));
     lx = v.x;
     ly = v.y;
   }
-  float w = ld_stream_f1(a.attn + si);
+  float w = ld_stream_f1(a.attn + GACB_INDEX(si, (long long)a.B * a.Q * a.H * a.LP, 3));
   // softmax as the reference's Softmax op does it: exp(x - max) / sum (src/gac/core/ops.py:1119-1125)
   if (a.softmax) w = __fdiv_rn(expf(__fsub_rn(w, norm.x)), norm.y);
   return geometry_of(lx, ly, w, level);
@@ -396,7 +406,7 @@ __global__ void __launch_bounds__(RowsCta<VT>::kThreads) msda_rows_kernel(const 
     int grow = -1;
     if (a.row_list) {
       const int e = (int)a.div_h((uint32_t)r);
-      if (e < a.row_list[-4]) grow = a.row_list[e] * a.H + (r - e * a.H);
+      if (e < a.row_list[-4]) grow = a.row_list[GACB_INDEX(e, (long long)a.B * a.Q, 6)] * a.H + (r - e * a.H);
     } else if (r < a.total_rows) {
       const RowId id = decode_row(a, r);
       grow = (int)id.grow;
@@ -442,13 +452,13 @@ __global__ void __launch_bounds__(RowsCta<VT>::kThreads) msda_rows_kernel(const 
         make_packed<FUSED>(a, grow, s0 + s, lvl, levels[lvl], a.softmax ? row_norm[rl] : make_float2(0.0f, 1.0f), f,
                            word);
       }
-      factors[rl * stride + s] = f;
-      words[rl * stride + s] = word;
+      factors[GACB_INDEX(rl * stride + s, rows_cta * stride, 2)] = f;
+      words[GACB_INDEX(rl * stride + s, rows_cta * stride, 2)] = word;
     }
     __syncthreads();
     for (int j = 0; j < J; ++j) {
       const int rl = j * RPI + grp;
-      const int grow = row_global[rl];
+      const int grow = row_global[GACB_INDEX(rl, rows_cta, 1)];
       if (grow < 0) continue;
       if (s0 == 0) {
 #pragma unroll
@@ -457,6 +467,10 @@ __global__ void __launch_bounds__(RowsCta<VT>::kThreads) msda_rows_kernel(const 
       // channel 0 of this lane in texel 0 of batch b, head h
       const RowId id = row_from_global(a, grow);
       const VT *base = static_cast<const VT *>(a.value) + (id.b * a.S * a.H + id.h) * a.D + lane * CPL;
+#if GACB_CHECKED
+      const long long base_off = (long long)(id.b * a.S * a.H + id.h) * a.D + lane * CPL;
+      const long long value_elems = (long long)a.B * a.S * a.H * a.D;
+#endif
       const float4 *fr = factors + rl * stride;
       const uint32_t *wr = words + rl * stride;
       for (int s = 0; s < CLP; s += kUnroll) {
@@ -467,15 +481,15 @@ __global__ void __launch_bounds__(RowsCta<VT>::kThreads) msda_rows_kernel(const 
           // the level (hence the row pitch) of a sample is the same for the whole CTA
           const int lvl = min((int)a.div_p((uint32_t)(s0 + s + u)), a.L - 1);
           const int pitch = a.lvl_w[lvl] * hd;
-          f[u] = fr[s + u];
-          const uint32_t word = wr[s + u];
+          f[u] = fr[GACB_INDEX(s + u, stride, 2)];
+          const uint32_t word = wr[GACB_INDEX(s + u, stride, 2)];
           const int o00 = (int)(word >> 2) * hd;
           const int dx = (int)(word & 1u) * hd;
           const int dy = (int)((word >> 1) & 1u) * pitch;
-          v[u][0] = Tap<VT, CPL>::load(base, o00);
-          v[u][1] = Tap<VT, CPL>::load(base, o00 + dx);
-          v[u][2] = Tap<VT, CPL>::load(base, o00 + dy);
-          v[u][3] = Tap<VT, CPL>::load(base, o00 + dy + dx);
+          v[u][0] = Tap<VT, CPL>::load(base, GACB_TAP(o00));
+          v[u][1] = Tap<VT, CPL>::load(base, GACB_TAP(o00 + dx));
+          v[u][2] = Tap<VT, CPL>::load(base, GACB_TAP(o00 + dy));
+          v[u][3] = Tap<VT, CPL>::load(base, GACB_TAP(o00 + dy + dx));
         }
 #if GACB_MSDA_FORCE_BATCH
 #pragma unroll
@@ -492,7 +506,7 @@ __global__ void __launch_bounds__(RowsCta<VT>::kThreads) msda_rows_kernel(const 
         }
       }
       if (s0 + cl == a.LP) {
-        float *dst = a.out + (long long)grow * a.D + lane * CPL;
+        float *dst = a.out + GACB_INDEX((long long)grow * a.D + lane * CPL, (long long)a.B * a.Q * a.H * a.D - CPL + 1, 5);
 #pragma unroll
         for (int c = 0; c < CPL; c += 4)
           st_stream_f4(dst + c, make_float4(acc[c], acc[c + 1], acc[c + 2], acc[c + 3]));
@@ -717,7 +731,7 @@ __global__ void __launch_bounds__(kTileThreads, 2) msda_tile_kernel(const __grid
           for (int u = 0; u < kTileBatch; ++u) {
             f[u] = fr[s + u];
             const uint32_t word = wr[s + u];
-            const float *p = wbase + ((word >> 20) & 0x3ffu) * kTileD;
+            const float *p = wbase + GACB_INDEX((word >> 20) & 0x3ffu, kWinH * kWinW - (word & 1u) - ((word >> 1) & 1u) * kWinW, 4) * kTileD;
             const int dx = (word & 1u) ? kTileD : 0;
             const int dy = (word & 2u) ? kWinW * kTileD : 0;
             v[u][0] = *reinterpret_cast<const float4 *>(p);
@@ -744,7 +758,8 @@ __global__ void __launch_bounds__(kTileThreads, 2) msda_tile_kernel(const __grid
             f[u] = fr[s + u];
             const uint32_t word = wr[s + u];
             const bool in = (word >> 31) != 0u;
-            const float *p = in ? wbase + ((word >> 20) & 0x3ffu) * kTileD : gbase + (size_t)((word >> 2) & 0x3ffffu) * hd;
+            const float *p = in ? wbase + GACB_INDEX((word >> 20) & 0x3ffu, kWinH * kWinW, 4) * kTileD
+                                : gbase + (size_t)GACB_INDEX((word >> 2) & 0x3ffffu, a.S - (word & 1u) - ((word >> 1) & 1u) * W, 4) * hd;
             const int dx = (word & 1u) ? (in ? kTileD : hd) : 0;
             const int dy = (word & 2u) ? (in ? kWinW * kTileD : W * hd) : 0;
             v[u][0] = *reinterpret_cast<const float4 *>(p);
@@ -761,7 +776,8 @@ __global__ void __launch_bounds__(kTileThreads, 2) msda_tile_kernel(const __grid
           }
         }
       }
-      st_stream_f4(a.out + (size_t)grow * a.D + lane * kTileCpl, make_float4(acc[0], acc[1], acc[2], acc[3]));
+      st_stream_f4(a.out + GACB_INDEX((long long)grow * a.D + lane * kTileCpl, (long long)a.B * a.Q * a.H * a.D - kTileCpl + 1, 5),
+                   make_float4(acc[0], acc[1], acc[2], acc[3]));
     }
     if (chunk + kChunkRows < kTileRows) __syncthreads();   // this chunk's records are consumed
   }
@@ -790,9 +806,10 @@ __global__ void __launch_bounds__(kThreads) msda_generic_kernel(const __grid_con
     const TapEntry t = make_entry<FUSED>(a, id, s, norm);
 #pragma unroll
     for (int k = 0; k < 4; ++k)
-      if (t.c[k] != 0.0f) acc = fmaf((float)value[t.off[k]], t.c[k], acc);
+      if (t.c[k] != 0.0f)
+        acc = fmaf((float)value[GACB_INDEX(t.off[k], (long long)a.B * a.S * a.H * a.D - ch, 4)], t.c[k], acc);
   }
-  a.out[id.grow * a.D + ch] = acc;
+  a.out[GACB_INDEX(id.grow * a.D + ch, (long long)a.B * a.Q * a.H * a.D, 5)] = acc;
 }
 
 // Visible (b, q) pairs of the query range, appended to list[] (count in list[-4]); a warp appends with one atomic.
@@ -1172,6 +1189,10 @@ static int msda_offsets_impl(const void *value, int value_dtype, const float *of
                 count, (long long)B * Q * H * L * P * 2);
   a.normalizer = normalizer;
   a.reference = reference;
+  a.norm_elems = 1;
+  for (int k = 0; k < 6; ++k) a.norm_elems *= norm_shape[k];
+  a.ref_elems = 1;
+  for (int k = 0; k < coord_rank; ++k) a.ref_elems *= ref_shape[k];
   a.coord_rank = n;
   a.reference_first = reference_first ? 1 : 0;
   a.softmax = softmax ? 1 : 0;
@@ -1278,6 +1299,17 @@ GACB_API int gacb_cast_f32_to_bf16(const float *src, void *dst, size_t count, vo
       src, static_cast<__nv_bfloat16 *>(dst), count);
   return check_cuda(cudaGetLastError(), "cast_f32_to_bf16 launch");
 }
+
+namespace gacb {
+int msda_check_record(unsigned int out[2]) {
+  out[0] = out[1] = 0;
+#if GACB_CHECKED
+  return check_cuda(cudaMemcpyFromSymbol(out, g_check_record, 2 * sizeof(unsigned int)), "cudaMemcpyFromSymbol(check record)");
+#else
+  return GACB_OK;
+#endif
+}
+}  // namespace gacb
 
 GACB_API int gacb_msda_tile_path(int mode) {
   const int previous = g_tile_path.load();

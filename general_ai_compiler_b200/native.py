@@ -31,6 +31,7 @@ DCN_BF16 = 2
 DCN_REUSE_WEIGHTS = 0x100   # GACB_DCN_REUSE_WEIGHTS
 DCN_REUSE_INPUT = 0x200     # GACB_DCN_REUSE_INPUT
 DCN_MATH_MODES = {"f32x3": DCN_F32X3, "tf32": DCN_TF32, "bf16": DCN_BF16}
+DCN_TEST_DROP_WEIGHT_COPIES = 0x400   # fault-injection build only (-DGACB_DCN_FAULT_INJECT=1)
 
 _vp = ctypes.c_void_p
 _i = ctypes.c_int
@@ -86,6 +87,7 @@ SIGNATURES = {
     "gacb_dcnv2_forward_static": (_i, [_vp] * 6 + [_i] * 18 + [_vp, _vp]),
     "gacb_msda_launch_geometry": (_i, [_i, _ip] + [_i] * 9 + [ctypes.POINTER(LaunchGeometry)]),
     "gacb_dcnv2_launch_geometry": (_i, [_i] * 18 + [ctypes.POINTER(LaunchGeometry)]),
+    "gacb_checked_violations": (_i, [ctypes.POINTER(ctypes.c_uint), ctypes.POINTER(ctypes.c_uint)]),
     "gacb_status_from_word": (_i, [ctypes.c_int32]),
     "gacb_read_status_word": (_i, [_vp, _vp]),
     "gacb_cast_f32_to_bf16": (_i, [_vp, _vp, _sz, _vp]),
@@ -93,6 +95,8 @@ SIGNATURES = {
 }
 
 _lib = None
+CHECKED_LIB_PATH = LIB_PATH.with_name("libgacb_checked.so")          # -DGACB_CHECKED=1
+FAULT_LIB_PATH = LIB_PATH.with_name("libgacb_faultinject.so")        # -DGACB_DCN_FAULT_INJECT=1, short spin limit
 
 
 def load() -> ctypes.CDLL:
@@ -161,3 +165,41 @@ def dcnv2_launch_geometry(n, Cin, H, W, Cout, Kh, Kw, stride, padding, dilation,
                                            sm_count, ctypes.byref(geo))
     check(rc, "gacb_dcnv2_launch_geometry")
     return geo
+
+
+def _bind(lib: ctypes.CDLL, path) -> ctypes.CDLL:
+    for name, (res, args) in SIGNATURES.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError as exc:
+            raise DeviceUnavailableError(f"{path} does not export {name}; rebuild it") from exc
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+class use_library:
+    """Context manager that routes every call of this module (and so of ``ops`` and ``CudaSession``) through
+    another build of the library -- the checked build or the fault-injection build -- and restores the normal one
+    afterwards.  For tests; not thread-safe."""
+
+    _cache: dict = {}
+
+    def __init__(self, path) -> None:
+        self.path = str(path)
+
+    def __enter__(self) -> ctypes.CDLL:
+        global _lib
+        load()
+        if self.path not in self._cache:
+            try:
+                self._cache[self.path] = _bind(ctypes.CDLL(self.path), self.path)
+            except OSError as exc:
+                raise DeviceUnavailableError(f"cannot load {self.path}: {exc}") from exc
+        self._previous = _lib
+        _lib = self._cache[self.path]
+        return _lib
+
+    def __exit__(self, *_):
+        global _lib
+        _lib = self._previous

@@ -556,7 +556,7 @@ def dcnv2_workspace_bytes(n, Cin, H, W, Cout, Kh, Kw, stride, padding, dilation,
 def dcnv2_forward(x, offset, mask, weight, bias=None, *, stride=(1, 1), padding=(0, 0), dilation=(1, 1),
                   groups=1, deform_groups=1, math="f32x3", out=None, n_range=None, workspace=None,
                   status_word=None, stream=None, mask_is_logits=False, batch_norm=None, relu=False, row_range=None,
-                  pixel_range=None, reuse_weights=False, reuse_input=False):
+                  pixel_range=None, reuse_weights=False, reuse_input=False, test_flags=0):
     """DCNv2 on device tensors (all float32, NCHW / OIHW).  ``math`` selects the
     tensor-core product: "f32x3" (fp32-faithful), "tf32" or "bf16".
 
@@ -571,7 +571,10 @@ def dcnv2_forward(x, offset, mask, weight, bias=None, *, stride=(1, 1), padding=
 
     ``reuse_weights`` / ``reuse_input`` promise that ``workspace`` still holds the
     packed weights / the channel-last copy of ``x`` from an earlier call (same
-    tensors' contents, shapes and ``math``); the call then skips that step."""
+    tensors' contents, shapes and ``math``); the call then skips that step.
+    ``test_flags`` is OR-ed into the library's ``math_mode`` argument; the only bit defined,
+    ``native.DCN_TEST_DROP_WEIGHT_COPIES``, is understood by the fault-injection build alone (the normal
+    library refuses it) and makes a bounded wait of the kernel run out."""
     torch = _torch()
     lib = native.load()
     if math not in native.DCN_MATH_MODES:
@@ -613,7 +616,7 @@ def dcnv2_forward(x, offset, mask, weight, bias=None, *, stride=(1, 1), padding=
     ws_ptr = workspace.data_ptr() if workspace is not None else None
     ws_len = workspace.numel() * workspace.element_size() if workspace is not None else 0
     dims = (N, Cin, H, W, Cout, Kh, Kw, stride[0], stride[1], padding[0], padding[1], dilation[0], dilation[1],
-            groups, deform_groups, n0, n1, native.DCN_MATH_MODES[math] | reuse, ws_ptr, ws_len,
+            groups, deform_groups, n0, n1, native.DCN_MATH_MODES[math] | reuse | int(test_flags), ws_ptr, ws_len,
             status_word.data_ptr() if status_word is not None else None, _stream_ptr(stream))
     bias_ptr = bias.data_ptr() if bias is not None else None
     if (row_range is not None or pixel_range is not None) and (mask_is_logits or batch_norm is not None or relu):

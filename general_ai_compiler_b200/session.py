@@ -223,7 +223,8 @@ class CudaSession:
                               workspace=self._workspaces.get(node.id), status_word=self._status,
                               stream=self._stream, mask_is_logits=bool(node.attrs.get("mask_is_logits", False)),
                               relu=bool(node.attrs.get("relu", False)), batch_norm=batch_norm,
-                              reuse_weights=self._reuse_weights(node, node.inputs[3]))
+                              reuse_weights=self._reuse_weights(node, node.inputs[3]),
+                              test_flags=int(opts.get("dcn_test_flags", 0)))
             self._weights_packed.add(node.id)
             return
         value = args[0]

@@ -309,6 +309,16 @@ int gacb_dcnv2_launch_geometry(int n, int Cin, int H, int W, int Cout, int Kh, i
                                int dh, int dw, int groups, int deform_groups, int math_mode, int plain, int sm_count,
                                gacb_launch_geometry *out);
 
+/* Checked build.  A library compiled with -DGACB_CHECKED=1 (general_ai_compiler_b200.build.build_native(
+ * extra_flags=("-DGACB_CHECKED=1",), output=...)) range-checks every gather offset, record-table slot and output
+ * index inside its kernels against the extent of the tensor or table it addresses; an index outside is counted and
+ * the access is redirected to element 0 (or, for a store, dropped), so nothing faults.  *count = violations on
+ * the current device since the library was loaded, *last_site = the code of the last failing site (the source
+ * files list them).  Synchronises the device.  The normal build returns GACB_ERR_UNSUPPORTED.  It stands in for
+ * the static guards of the reference (guarded loads as control flow, native/lib/DeviceLowering.cpp:251-286;
+ * launch and lifetime validation, native/runtime/dispatch-plan.h:609-627) and for a memory checker. */
+int gacb_checked_violations(unsigned int *count, unsigned int *last_site);
+
 /* The device status word of the calls above, turned into a status.  (GAC reports a failed device step as a
  * `failed` session / a `status:"failed"` report with the failing stage: src/gac/execution/cuda.py:457-464,
  * native/runtime/cuda-run.cpp:685-703.)
