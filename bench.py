@@ -357,6 +357,23 @@ def bench_dcn(device, keys=("dcn_c4", "dcn_c5"), modes=("f32x3", "tf32", "bf16")
                     conv_offset(reuse_weights=True)
                     dcn_fused(reuse_weights=True)
 
+                # one buffer for the pair: the channel-last copy of X at its end, shared; each layer's weights in front
+                _, ws_conv_shared, ws_dcn_shared = ops.shared_input_workspaces(t["X"], 3 * k2, wl.cout, wl.kernel, wl.stride,
+                                                                               wl.padding, wl.dilation, wl.groups,
+                                                                               wl.deform_groups, math)
+
+                def chain_shared(**reuse):
+                    ops.conv2d_forward(t["X"], w_off, b_off, strides=wl.stride, pads=pads, dilations=wl.dilation, math=math,
+                                       split_at=2 * k2, out=off_out, workspace=ws_conv_shared, status_word=status,
+                                       stream=stream, input_at_end=True, **reuse)
+                    ops.dcnv2_forward(t["X"], off_out[0], off_out[1], t["W"], t["bias"], stride=wl.stride, padding=wl.padding,
+                                      dilation=wl.dilation, math=math, out=y, workspace=ws_dcn_shared, status_word=status,
+                                      stream=stream, mask_is_logits=True, batch_norm=bn, relu=True, input_at_end=True,
+                                      reuse_input=True, **reuse)
+
+                def chain_shared_steady():
+                    chain_shared(reuse_weights=True)
+
                 def dcn_prepacked():
                     ops.dcnv2_forward(t["X"], t["offset"], t["mask"], t["W"], t["bias"], stride=wl.stride, padding=wl.padding,
                                       dilation=wl.dilation, math=math, out=y, workspace=ws, status_word=status, stream=stream,
@@ -365,6 +382,8 @@ def bench_dcn(device, keys=("dcn_c4", "dcn_c5"), modes=("f32x3", "tf32", "bf16")
                 for name, fn, flops in (("conv_offset", conv_offset, 2.0 * wl.batch * 3 * k2 * wl.cin * k2 * ho * wo),
                                         ("conv_offset+dcn+bn+relu", chain, None),
                                         ("conv_offset+dcn+bn+relu/weights_prepacked", chain_steady, None),
+                                        ("conv_offset+dcn+bn+relu/shared_input_copy", chain_shared, None),
+                                        ("conv_offset+dcn+bn+relu/shared_input_copy+weights_prepacked", chain_shared_steady, None),
                                         ("weights_prepacked", dcn_prepacked, float(wl.flops))):
                     for _ in range(warmup):
                         fn()

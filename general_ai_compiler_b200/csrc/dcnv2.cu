@@ -562,6 +562,9 @@ struct UmmaArgs {
 // four tap coefficients (20 bytes per record).  With up to kMaxRecordSlots (kernel point, deformable group) pairs
 // per CTA the whole table is built once per tile; otherwise each of the four producer groups owns one slot.
 constexpr int kMaxRecordSlots = 9;
+// Per output channel of the tile, staged in shared memory once: bias, BatchNorm mean, sqrt(variance + epsilon),
+// scale, BatchNorm bias (the epilogue would otherwise fetch them -- and take the square root -- per element).
+constexpr int kEpilogueParams = 5;
 constexpr int kRecordBytes = sizeof(uint32_t) + sizeof(float4);
 
 template <int MODE>
@@ -570,9 +573,12 @@ struct SmemLayout {
   static constexpr int kATile = kTileM * T::kRowBytes;   // per part
   static size_t a_stage_bytes() { return (size_t)T::kParts * kATile; }
   static size_t b_stage_bytes(int tile_n) { return (size_t)T::kParts * tile_n * T::kRowBytes; }
-  static size_t total(int tile_n, int record_slots, int a_stages = kAStages) {
+  // ep_rows = rows of the epilogue parameter table: kEpilogueParams with BatchNorm folded in, else 0; every KB not
+  // taken here stays L1 for the gathers
+  static size_t total(int tile_n, int record_slots, int a_stages = kAStages, int ep_rows = kEpilogueParams) {
     return 1024 /*alignment slack*/ + a_stages * a_stage_bytes() + kBStages * b_stage_bytes(tile_n) +
-           (size_t)record_slots * kTileM * kRecordBytes + 256 /*barriers, tmem slot, abort flag*/;
+           (size_t)record_slots * kTileM * kRecordBytes + 256 /*barriers, tmem slot, abort flag*/ +
+           (size_t)ep_rows * ((tile_n + 31) / 32 * 32) * sizeof(float);
   }
 };
 
@@ -626,6 +632,21 @@ __device__ __forceinline__ uint32_t pack_bf16x2(__nv_bfloat16 lo, __nv_bfloat16 
   return (uint32_t)__bfloat16_as_ushort(lo) | ((uint32_t)__bfloat16_as_ushort(hi) << 16);
 }
 
+// Epilogue parameter table of one tile's output channels (BatchNorm calls only); padding columns get neutral values.
+__device__ __noinline__ void fill_epilogue_table(const DcnArgs &a, float *table, int pitch, int group, int n_tile, int tile_n) {
+  const int cout_g = a.Cout / a.groups;
+  const int cols = min(tile_n, cout_g - n_tile * tile_n);
+  for (int c = threadIdx.x; c < pitch; c += blockDim.x) {
+    const int co = group * cout_g + n_tile * tile_n + c;
+    const bool live = c < cols;
+    table[0 * pitch + c] = (live && a.bias) ? __ldg(a.bias + co) : 0.0f;
+    table[1 * pitch + c] = live ? __ldg(a.bn_mean + co) : 0.0f;
+    table[2 * pitch + c] = live ? __fsqrt_rn(__fadd_rn(__ldg(a.bn_var + co), a.bn_eps)) : 1.0f;
+    table[3 * pitch + c] = live ? __ldg(a.bn_scale + co) : 1.0f;
+    table[4 * pitch + c] = live ? __ldg(a.bn_bias + co) : 0.0f;
+  }
+}
+
 // PLAIN = plain convolution (no offset/mask operands): every sample is one texel at an integer position, so the
 // producers fetch one tap instead of four and copy instead of blending.
 template <int MODE, bool PLAIN, bool NARROW>
@@ -660,6 +681,10 @@ __global__ void __launch_bounds__(CtaShape<NARROW>::kThreads, CtaShape<NARROW>::
   // bars: full_a[SA] | empty_a[SA] | full_b[SB] | empty_b[SB] | acc_full
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * SA + 2 * SB + 1);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  // epilogue parameter table [rows][ep_stride] right after the barrier block (recomputed where it is used, so that
+  // nothing of it stays live through the K loop)
+  auto ep_table = [&]() { return reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(bars) + 256); };
+  auto ep_pitch = [&]() { return (u.tile_n + 31) / 32 * 32; };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int m_tile = blockIdx.x, n_tile = blockIdx.y, group = blockIdx.z;
@@ -693,6 +718,9 @@ __global__ void __launch_bounds__(CtaShape<NARROW>::kThreads, CtaShape<NARROW>::
     fence_mbar_init();
   }
   if (warp == kMmaWarp) tmem_alloc(smem_u32(tmem_slot), (uint32_t)u.tmem_cols);
+  // BatchNorm folded in: per output channel of the tile {bias, mean, sqrt(variance + epsilon), scale, BatchNorm bias}
+  // go to shared memory once, instead of five loads and a square root per element in the epilogue
+  if (a.bn_scale != nullptr) fill_epilogue_table(a, ep_table(), ep_pitch(), group, n_tile, u.tile_n);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -953,8 +981,7 @@ __global__ void __launch_bounds__(CtaShape<NARROW>::kThreads, CtaShape<NARROW>::
       const int cols = min(tile_n, cout_g - n_tile * tile_n);   // the last tile of a group may carry padding columns
       // Everything the store loop needs, in registers: per-channel parameters are fetched for the whole slab before
       // the stores, so that no load sits between two stores.
-      const float *bias = a.bias, *bn_scale = a.bn_scale, *bn_bias = a.bn_bias, *bn_mean = a.bn_mean, *bn_var = a.bn_var;
-      const float bn_eps = a.bn_eps;
+      const float *bias = a.bias, *bn_scale = a.bn_scale;
       const bool relu = a.relu != 0;
       const int n_img = a.n_begin + img;
       const int split_at = a.y_split != nullptr ? a.split_at : a.Cout;      // channels below it go to y
@@ -985,22 +1012,24 @@ __global__ void __launch_bounds__(CtaShape<NARROW>::kThreads, CtaShape<NARROW>::
           }
         }
         // bias, then BatchNorm ((v - mean) / sqrt(var + eps) * scale + bias), then ReLU: dcn_epilogue's arithmetic
-        if (bias != nullptr) {
+        if (bn_scale != nullptr) {
+          // bias, (v - mean) / sqrt(var + eps) * scale + BatchNorm bias, per-channel values from the table
+          const float *ep_params = ep_table();
+          const int ep_stride = ep_pitch();
+          const float *bs = ep_params + col, *mean = bs + ep_stride, *sd = mean + ep_stride, *scale = sd + ep_stride,
+                      *shift = scale + ep_stride;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float v = __uint_as_float(r[j]);
+            if (bias != nullptr) v = __fadd_rn(v, bs[j]);
+            v = __fdiv_rn(__fsub_rn(v, mean[j]), sd[j]);
+            r[j] = __float_as_uint(__fadd_rn(__fmul_rn(v, scale[j]), shift[j]));
+          }
+        } else if (bias != nullptr) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const float b = col + j < cols ? __ldg(bias + co_base + col + j) : 0.0f;
             r[j] = __float_as_uint(__fadd_rn(__uint_as_float(r[j]), b));
-          }
-        }
-        if (bn_scale != nullptr) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (col + j < cols) {
-              const int co = co_base + col + j;
-              const float sd = __fsqrt_rn(__fadd_rn(__ldg(bn_var + co), bn_eps));
-              const float v = __fdiv_rn(__fsub_rn(__uint_as_float(r[j]), __ldg(bn_mean + co)), sd);
-              r[j] = __float_as_uint(__fadd_rn(__fmul_rn(v, __ldg(bn_scale + co)), __ldg(bn_bias + co)));
-            }
           }
         }
         if (relu) {
@@ -1142,7 +1171,8 @@ UmmaLaunch shape_umma_launch(const DcnArgs &a, const UmmaPlan &p, int sms, UmmaA
   UmmaLaunch l;
   l.narrow = p.tile_n <= 64 && (long long)p.m_tiles * p.n_tiles * a.groups > sms;
   u.record_slots = u.precomputed ? wanted : (l.narrow ? CtaShape<true>::kGroups : kGroups);
-  l.smem = SmemLayout<MODE>::total(p.tile_n, u.record_slots, l.narrow ? CtaShape<true>::kAStages : kAStages);
+  l.smem = SmemLayout<MODE>::total(p.tile_n, u.record_slots, l.narrow ? CtaShape<true>::kAStages : kAStages,
+                                   a.bn_scale ? kEpilogueParams : 0);
   l.grid = dim3(p.m_tiles, p.n_tiles, a.groups);
   l.threads = l.narrow ? CtaShape<true>::kThreads : CtaShape<false>::kThreads;
   return l;
@@ -1150,12 +1180,16 @@ UmmaLaunch shape_umma_launch(const DcnArgs &a, const UmmaPlan &p, int sms, UmmaA
 
 template <int MODE>
 int launch_umma(const DcnArgs &a, const UmmaPlan &p, void *workspace, int32_t *status, cudaStream_t stream,
-                int reuse_flags = 0) {
+                int reuse_flags = 0, size_t workspace_bytes = 0) {
   using T = ModeTraits<MODE>;
-  unsigned char *blob = static_cast<unsigned char *>(workspace) + p.xt_bytes;
+  // workspace = [channel-last copy | packed weights], or with GACB_DCN_INPUT_AT_END [packed weights | ... | copy]
+  // with the copy in the last xt_bytes of the workspace (so that calls with different weights can share it)
+  const bool at_end = (reuse_flags & GACB_DCN_INPUT_AT_END) != 0;
+  unsigned char *ws = static_cast<unsigned char *>(workspace);
+  unsigned char *blob = at_end ? ws : ws + p.xt_bytes;
   const int HW = a.H * a.W;
   using XtT = typename std::conditional<T::kXtBytes == 4, float, __nv_bfloat16>::type;
-  XtT *xt = static_cast<XtT *>(workspace);
+  XtT *xt = reinterpret_cast<XtT *>(at_end ? ws + (workspace_bytes - p.xt_bytes) : ws);
   const int n_images = a.n_end - a.n_begin;
   const uintptr_t x_addr = reinterpret_cast<uintptr_t>(a.x);
   if (reuse_flags & GACB_DCN_REUSE_INPUT) {
@@ -1179,7 +1213,7 @@ int launch_umma(const DcnArgs &a, const UmmaPlan &p, void *workspace, int32_t *s
 
   UmmaArgs u;
   u.d = a;
-  u.xt = workspace;
+  u.xt = xt;
   u.blob = blob;
   u.status = status;
   u.drop_weight_copies = (reuse_flags & kTestDropWeightCopies) ? 1 : 0;
@@ -1300,7 +1334,8 @@ static int dcnv2_forward_impl(const float *x, const float *offset, const float *
   DcnArgs a{};
   const int reuse_flags = math_mode & ~0xff;
   math_mode &= 0xff;
-  if (reuse_flags & ~(GACB_DCN_REUSE_WEIGHTS | GACB_DCN_REUSE_INPUT | (GACB_DCN_FAULT_INJECT ? kTestDropWeightCopies : 0)))
+  if (reuse_flags & ~(GACB_DCN_REUSE_WEIGHTS | GACB_DCN_REUSE_INPUT | GACB_DCN_INPUT_AT_END |
+                      (GACB_DCN_FAULT_INJECT ? kTestDropWeightCopies : 0)))
     return fail(GACB_ERR_INVALID_ARGUMENT, "dcnv2: unknown flag bits 0x%x in math_mode", reuse_flags);
   int rc = validate(a, x, offset, mask, w, bias, y, N, Cin, H, W, Cout, Kh, Kw, sh, sw, ph, pw, dh, dw, groups,
                     deform_groups, n_begin, n_end, math_mode, extras.pad_bottom, extras.pad_right, extras.plain);
@@ -1341,10 +1376,12 @@ static int dcnv2_forward_impl(const float *x, const float *offset, const float *
       return fail(GACB_ERR_INVALID_ARGUMENT, "dcnv2: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
     if (reinterpret_cast<uintptr_t>(workspace) % 256)
       return fail(GACB_ERR_INVALID_ARGUMENT, "dcnv2: workspace must be 256-byte aligned");
+    if ((reuse_flags & GACB_DCN_INPUT_AT_END) && workspace_bytes % 256)
+      return fail(GACB_ERR_INVALID_ARGUMENT, "dcnv2: with GACB_DCN_INPUT_AT_END workspace_bytes must be a multiple of 256");
     switch (math_mode) {
-      case MODE_BF16: return launch_umma<MODE_BF16>(a, p, workspace, status_word, stream, reuse_flags);
-      case MODE_TF32: return launch_umma<MODE_TF32>(a, p, workspace, status_word, stream, reuse_flags);
-      default: return launch_umma<MODE_F32X3>(a, p, workspace, status_word, stream, reuse_flags);
+      case MODE_BF16: return launch_umma<MODE_BF16>(a, p, workspace, status_word, stream, reuse_flags, workspace_bytes);
+      case MODE_TF32: return launch_umma<MODE_TF32>(a, p, workspace, status_word, stream, reuse_flags, workspace_bytes);
+      default: return launch_umma<MODE_F32X3>(a, p, workspace, status_word, stream, reuse_flags, workspace_bytes);
     }
   }
   const long long total = (long long)Cout * a.m_count;
@@ -1552,5 +1589,27 @@ GACB_API int gacb_dcnv2_launch_geometry(int n, int Cin, int H, int W, int Cout, 
   snprintf(out->kernel, sizeof(out->kernel), "dcn_umma_kernel<%s,%s,%s>",
            math_mode == MODE_BF16 ? "bf16" : (math_mode == MODE_TF32 ? "tf32" : "f32x3"), plain ? "plain" : "deform",
            l.narrow ? "narrow" : "wide");
+  return GACB_OK;
+}
+
+GACB_API int gacb_dcnv2_workspace_parts(int n, int Cin, int H, int W, int Cout, int Kh, int Kw, int sh, int sw, int pad_top,
+                                        int pad_left, int pad_bottom, int pad_right, int dh, int dw, int groups,
+                                        int deform_groups, int math_mode, int plain, size_t *input_copy_bytes,
+                                        size_t *weights_bytes) {
+  if (!input_copy_bytes || !weights_bytes) return fail(GACB_ERR_INVALID_ARGUMENT, "workspace_parts: NULL output");
+  *input_copy_bytes = *weights_bytes = 0;
+  DcnArgs a{};
+  math_mode &= 0xff;
+  if (n <= 0) return GACB_OK;
+  int rc = validate(a, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, n, Cin, H, W, Cout, Kh, Kw, sh, sw, pad_top,
+                    pad_left, dh, dw, groups, deform_groups, 0, 0, math_mode, pad_bottom, pad_right, plain != 0);
+  if (rc != GACB_OK) return rc;
+  a.n_begin = 0;
+  a.n_end = n;
+  a.m_count = n * a.Ho * a.Wo;
+  UmmaPlan p;
+  if (!plan_umma(a, math_mode, p)) return GACB_OK;      // CUDA-core kernel: no workspace at all
+  *input_copy_bytes = p.xt_bytes;
+  *weights_bytes = p.blob_bytes;
   return GACB_OK;
 }

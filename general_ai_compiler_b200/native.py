@@ -30,6 +30,7 @@ DCN_TF32 = 1
 DCN_BF16 = 2
 DCN_REUSE_WEIGHTS = 0x100   # GACB_DCN_REUSE_WEIGHTS
 DCN_REUSE_INPUT = 0x200     # GACB_DCN_REUSE_INPUT
+DCN_INPUT_AT_END = 0x800    # GACB_DCN_INPUT_AT_END
 DCN_MATH_MODES = {"f32x3": DCN_F32X3, "tf32": DCN_TF32, "bf16": DCN_BF16}
 DCN_TEST_DROP_WEIGHT_COPIES = 0x400   # fault-injection build only (-DGACB_DCN_FAULT_INJECT=1)
 
@@ -85,6 +86,7 @@ SIGNATURES = {
                                  + [_i] * 18 + [_vp, _sz, _vp, _vp]),
     "gacb_dcnv2_workspace_bytes": (_sz, [_i] * 16),
     "gacb_dcnv2_forward_static": (_i, [_vp] * 6 + [_i] * 18 + [_vp, _vp]),
+    "gacb_dcnv2_workspace_parts": (_i, [_i] * 19 + [ctypes.POINTER(_sz), ctypes.POINTER(_sz)]),
     "gacb_msda_launch_geometry": (_i, [_i, _ip] + [_i] * 9 + [ctypes.POINTER(LaunchGeometry)]),
     "gacb_dcnv2_launch_geometry": (_i, [_i] * 18 + [ctypes.POINTER(LaunchGeometry)]),
     "gacb_checked_violations": (_i, [ctypes.POINTER(ctypes.c_uint), ctypes.POINTER(ctypes.c_uint)]),

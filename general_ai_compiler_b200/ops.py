@@ -534,10 +534,47 @@ def msda_group_forward(value, locations, attention, spatial_shapes, *, group=1, 
     return result
 
 
-def _reuse_bits(reuse_weights: bool, reuse_input: bool, workspace) -> int:
-    if (reuse_weights or reuse_input) and workspace is None:
-        raise EvaluationError("reuse_weights/reuse_input need the caller's workspace of the earlier call")
-    return (native.DCN_REUSE_WEIGHTS if reuse_weights else 0) | (native.DCN_REUSE_INPUT if reuse_input else 0)
+def _reuse_bits(reuse_weights: bool, reuse_input: bool, workspace, input_at_end: bool = False) -> int:
+    if (reuse_weights or reuse_input or input_at_end) and workspace is None:
+        raise EvaluationError("reuse_weights/reuse_input/input_at_end need the caller's workspace")
+    return ((native.DCN_REUSE_WEIGHTS if reuse_weights else 0) | (native.DCN_REUSE_INPUT if reuse_input else 0)
+            | (native.DCN_INPUT_AT_END if input_at_end else 0))
+
+
+def workspace_parts(n, Cin, H, W, Cout, Kh, Kw, stride, pads, dilation, groups, deform_groups, math, plain=False):
+    """(bytes of the channel-last input copy, bytes of the packed weights) of a DCNv2 (``plain=False``, two pads)
+    or Conv2D (``plain=True``, four pads) call on ``n`` images; both 0 when the shape runs on the CUDA-core kernel."""
+    pads = tuple(pads) if len(pads) == 4 else (pads[0], pads[1], pads[0], pads[1])
+    copy_bytes, weight_bytes = ctypes.c_size_t(0), ctypes.c_size_t(0)
+    rc = native.load().gacb_dcnv2_workspace_parts(n, Cin, H, W, Cout, Kh, Kw, stride[0], stride[1], *pads, dilation[0],
+                                                  dilation[1], groups, deform_groups, native.DCN_MATH_MODES[math],
+                                                  1 if plain else 0, ctypes.byref(copy_bytes), ctypes.byref(weight_bytes))
+    native.check(rc, "gacb_dcnv2_workspace_parts")
+    return int(copy_bytes.value), int(weight_bytes.value)
+
+
+def shared_input_workspaces(x, conv_cout, dcn_cout, kernel, stride, padding, dilation, groups=1, deform_groups=1,
+                            math="f32x3"):
+    """One device buffer for the ``conv_offset`` -> DCNv2 pair of an R101-DCN bottleneck (both read the same ``x``):
+    returns ``(buffer, conv_workspace, dcn_workspace)``, two views that end at the same address.  Call
+    ``conv2d_forward(..., workspace=conv_workspace, input_at_end=True)`` first (it makes the channel-last copy of
+    ``x``), then ``dcnv2_forward(..., workspace=dcn_workspace, input_at_end=True, reuse_input=True)``; add
+    ``reuse_weights=True`` to both once each has packed its weights.  The block then pays for one copy, and in the
+    steady state for no packing.  Returns ``(None, None, None)`` when the shapes run on the CUDA-core kernels."""
+    torch = _torch()
+    n, cin, h, w = x.shape
+    kh, kw = kernel
+    copy_c, weights_c = workspace_parts(n, cin, h, w, conv_cout, kh, kw, stride, (padding[0], padding[1]) * 2, dilation, 1,
+                                        1, math, plain=True)
+    copy_d, weights_d = workspace_parts(n, cin, h, w, dcn_cout, kh, kw, stride, padding, dilation, groups, deform_groups,
+                                        math)
+    if not copy_c or not copy_d:
+        return None, None, None
+    assert copy_c == copy_d, "both layers copy the same images in the same element type"
+    first = -(-weights_c // 256) * 256
+    total = first + -(-weights_d // 256) * 256 + copy_d
+    buf = torch.empty(total, dtype=torch.uint8, device=x.device)
+    return buf, buf, buf[first:]
 
 
 def dcn_output_hw(H, W, Kh, Kw, stride, padding, dilation):
@@ -556,7 +593,7 @@ def dcnv2_workspace_bytes(n, Cin, H, W, Cout, Kh, Kw, stride, padding, dilation,
 def dcnv2_forward(x, offset, mask, weight, bias=None, *, stride=(1, 1), padding=(0, 0), dilation=(1, 1),
                   groups=1, deform_groups=1, math="f32x3", out=None, n_range=None, workspace=None,
                   status_word=None, stream=None, mask_is_logits=False, batch_norm=None, relu=False, row_range=None,
-                  pixel_range=None, reuse_weights=False, reuse_input=False, test_flags=0):
+                  pixel_range=None, reuse_weights=False, reuse_input=False, input_at_end=False, test_flags=0):
     """DCNv2 on device tensors (all float32, NCHW / OIHW).  ``math`` selects the
     tensor-core product: "f32x3" (fp32-faithful), "tf32" or "bf16".
 
@@ -610,7 +647,7 @@ def dcnv2_forward(x, offset, mask, weight, bias=None, *, stride=(1, 1), padding=
         n0, n1 = p0 // (Ho * Wo), (p0 // (Ho * Wo) if p1 == p0 else -(-p1 // (Ho * Wo)))
     need = dcnv2_workspace_bytes(n1 - n0, Cin, H, W, Cout, Kh, Kw, stride, padding, dilation, groups,
                                  deform_groups, math)
-    reuse = _reuse_bits(reuse_weights, reuse_input, workspace)
+    reuse = _reuse_bits(reuse_weights, reuse_input, workspace, input_at_end)
     if workspace is None and need:
         workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
     ws_ptr = workspace.data_ptr() if workspace is not None else None
@@ -666,7 +703,7 @@ def conv2d_workspace_bytes(n_images, Cin, H, W, Cout, Kh, Kw, strides, pads, dil
 
 def conv2d_forward(x, weight, bias=None, *, strides=(1, 1), pads=(0, 0, 0, 0), dilations=(1, 1), groups=1,
                    math="f32x3", relu=False, split_at=None, out=None, n_range=None, workspace=None,
-                   status_word=None, stream=None, reuse_weights=False, reuse_input=False):
+                   status_word=None, stream=None, reuse_weights=False, reuse_input=False, input_at_end=False):
     """Plain convolution on device tensors (float32, NCHW / OIHW) through the DCNv2 kernels with integer taps.
 
     ``split_at=c`` returns two tensors, channels ``[0, c)`` and ``[c, Cout)`` -- for BEVFormer's ``conv_offset``
@@ -713,7 +750,7 @@ def conv2d_forward(x, weight, bias=None, *, strides=(1, 1), pads=(0, 0, 0, 0), d
                 raise EvaluationError(f"Conv2D output must have shape {shape}")
     n0, n1 = (0, N) if n_range is None else (int(n_range[0]), int(n_range[1]))
     need = conv2d_workspace_bytes(n1 - n0, Cin, H, W, Cout, Kh, Kw, strides, pads, dilations, groups, math)
-    reuse = _reuse_bits(reuse_weights, reuse_input, workspace)
+    reuse = _reuse_bits(reuse_weights, reuse_input, workspace, input_at_end)
     if workspace is None and need:
         workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
     ws_ptr = workspace.data_ptr() if workspace is not None else None

@@ -64,6 +64,15 @@ typedef enum gacb_dcn_math {
  * on the CUDA-core kernel (workspace size 0). */
 #define GACB_DCN_REUSE_WEIGHTS 0x100
 #define GACB_DCN_REUSE_INPUT 0x200
+/*   GACB_DCN_INPUT_AT_END   the workspace layout is [packed weights | ... | channel-last copy] with the copy in the
+ *                           LAST input_copy_bytes of the workspace (workspace_bytes then a multiple of 256).  Two
+ *                           layers that read the same X -- `conv_offset` and the DCNv2 it feeds -- can then share
+ *                           one copy and still keep their own packed weights: give both calls workspaces that END
+ *                           at the same address (the second one starts after the first one's weights), let the
+ *                           first call make the copy and pass GACB_DCN_REUSE_INPUT to the second; with
+ *                           GACB_DCN_REUSE_WEIGHTS on both, a steady-state block pays one copy and no packing.
+ *                           gacb_dcnv2_workspace_parts gives the two sizes. */
+#define GACB_DCN_INPUT_AT_END 0x800
 
 int gacb_version(void);
 const char *gacb_last_error_string(void);
@@ -261,6 +270,14 @@ int gacb_dcnv2_pixels_forward(const float *x, const float *offset, const float *
 size_t gacb_dcnv2_workspace_bytes(int n, int Cin, int H, int W, int Cout, int Kh, int Kw, int sh,
                                   int sw, int ph, int pw, int dh, int dw, int groups,
                                   int deform_groups, int math_mode);
+
+/* The two parts of the workspace of gacb_dcnv2_forward (plain = 0; pad_bottom/pad_right = pad_top/pad_left) or
+ * gacb_conv2d_forward (plain = 1) for n images: the channel-last copy of the images and the packed weights, both 0
+ * when the shape runs on the CUDA-core kernel.  Their sum is what the *_workspace_bytes functions return. */
+int gacb_dcnv2_workspace_parts(int n, int Cin, int H, int W, int Cout, int Kh, int Kw, int sh, int sw, int pad_top,
+                               int pad_left, int pad_bottom, int pad_right, int dh, int dw, int groups,
+                               int deform_groups, int math_mode, int plain, size_t *input_copy_bytes,
+                               size_t *weights_bytes);
 
 /* DCNv2 forward for callers that may not allocate device memory.  (No counterpart in the reference: GAC's
  * runners allocate whatever a dispatch needs when they build their arena.)

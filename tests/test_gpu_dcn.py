@@ -236,6 +236,47 @@ def test_workspace_reuse_flags(dev):
     assert rc == -1 and "flag" in ops.native.last_error()
 
 
+@pytest.mark.parametrize("math", ["f32x3", "bf16"])
+def test_conv_offset_and_dcn_share_one_input_copy(dev, math):
+    """conv_offset and the DCNv2 it feeds read the same X: with the channel-last copy at the END of two workspaces
+    that end at the same address, the first call makes the copy, the second reuses it, and both keep their own
+    packed weights -- bit-identical to two calls with private workspaces, also in the steady state (nothing packed,
+    one copy per block)."""
+    torch, ops, device = dev
+    from general_ai_compiler_b200.bevformer import DcnWorkload
+
+    wl = DcnWorkload("shared", 2, 64, 21, 28, 96, seed=71)
+    c = _workload_case(wl)
+    t = {k: torch.from_numpy(np.ascontiguousarray(c[k])).to(device) for k in ("X", "W", "bias")}
+    w27 = (torch.randn((27, 64, 3, 3), device=device) * 0.05).contiguous()
+    b27 = torch.randn(27, device=device)
+    kw = dict(stride=(1, 1), padding=(1, 1), dilation=(1, 1), math=math)
+
+    def block(x, conv_ws=None, dcn_ws=None, **flags):
+        conv_flags = {k: v for k, v in flags.items() if k != "reuse_input"}
+        off, mask = ops.conv2d_forward(x, w27, b27, pads=(1, 1, 1, 1), math=math, split_at=18, workspace=conv_ws, **conv_flags)
+        y = ops.dcnv2_forward(x, off, mask, t["W"], t["bias"], mask_is_logits=True, workspace=dcn_ws, **kw, **flags)
+        torch.cuda.synchronize()
+        return off, mask, y
+
+    want = block(t["X"])
+    buf, conv_ws, dcn_ws = ops.shared_input_workspaces(t["X"], 27, 96, (3, 3), (1, 1), (1, 1), (1, 1), math=math)
+    assert buf is not None and conv_ws.data_ptr() % 256 == 0 and dcn_ws.data_ptr() % 256 == 0
+    assert conv_ws.data_ptr() + conv_ws.numel() == dcn_ws.data_ptr() + dcn_ws.numel()       # same end: same copy
+    copy_bytes, weights = ops.workspace_parts(2, 64, 21, 28, 96, 3, 3, (1, 1), (1, 1), (1, 1), 1, 1, math)
+    assert copy_bytes + weights == ops.dcnv2_workspace_bytes(2, 64, 21, 28, 96, 3, 3, (1, 1), (1, 1), (1, 1), 1, 1, math)
+    buf.fill_(0xA5)
+    got = block(t["X"], conv_ws, dcn_ws, input_at_end=True, reuse_input=True)
+    assert all(torch.equal(g, w) for g, w in zip(got, want))
+    steady = block(t["X"], conv_ws, dcn_ws, input_at_end=True, reuse_input=True, reuse_weights=True)
+    assert all(torch.equal(g, w) for g, w in zip(steady, want))
+    # the copy is really shared: a changed X is picked up by conv_offset's copy and seen by the DCNv2 that reuses it
+    x2 = (t["X"] * 0.5 + 0.25).contiguous()
+    want2 = block(x2)
+    got2 = block(x2, conv_ws, dcn_ws, input_at_end=True, reuse_input=True, reuse_weights=True)
+    assert all(torch.equal(g, w) for g, w in zip(got2, want2))
+
+
 def test_direct_and_tensor_paths_agree(dev):
     """Cin=64 with dense weights takes the tensor-core path; the same problem viewed as 4 groups of 16 channels
     (block-diagonal weights) cannot be tiled and takes the CUDA-core path.  Both must agree to the fp32 gate."""
