@@ -185,6 +185,9 @@ __global__ void __launch_bounds__(256) dcn_direct_kernel(const __grid_constant__
 // ----------------------------------------------------------------------------------------------
 
 constexpr int kTileM = 128;          // pixels per CTA tile = TMEM lanes
+#ifndef GACB_DCN_BLOCK_H
+#define GACB_DCN_BLOCK_H 8           // rows of the pixel blocks a whole-image call walks (0 = plain row-major order)
+#endif
 #ifndef GACB_DCN_BATCH_BF16
 #define GACB_DCN_BATCH_BF16 2
 #endif
@@ -556,6 +559,7 @@ struct UmmaArgs {
   int precomputed;             // the table holds every (kernel point, deformable group) record of a tile
   unsigned b_stage_bytes;
   int drop_weight_copies;      // test build only (GACB_DCN_FAULT_INJECT): the loader skips every copy
+  int block_h, block_w;        // blocked pixel order of whole-image calls (PixelOrder); 0 = plain order
 };
 
 // Tap records live in shared memory as two arrays of record_slots x 128 entries: a packed geometry word and the
@@ -632,6 +636,39 @@ __device__ __forceinline__ uint32_t pack_bf16x2(__nv_bfloat16 lo, __nv_bfloat16 
   return (uint32_t)__bfloat16_as_ushort(lo) | ((uint32_t)__bfloat16_as_ushort(hi) << 16);
 }
 
+// Order of the output pixels along the M dimension of the implicit GEMM.  A call that covers whole images
+// (block_h > 0) walks every image in blocks of block_h rows x block_w columns, row-major inside a block, blocks
+// row-major over the image, ragged blocks at the right and bottom edges: a 128-row tile is then a compact
+// 8 x 16 patch of pixels whose taps fall on a small neighbourhood of the input (the nine kernel points and the
+// neighbouring pixels share texels), which is what L1 can hold.  A call restricted to rows or to a pixel run
+// keeps the plain (image, row, column) order.  Each output element is computed the same way in both orders.
+struct PixelOrder {
+  int plane_sel, pix_first, m_first;   // plain order: selected pixel f = m_first + m -> image f / plane_sel, ...
+  int block_h, block_w, Ho, Wo;        // blocked order when block_h > 0
+};
+
+__device__ __forceinline__ void pixel_of(const PixelOrder &o, int m, int &img, int &pix) {
+  if (o.block_h == 0) {
+    const int f = o.m_first + m;
+    img = f / o.plane_sel;
+    pix = o.pix_first + f - img * o.plane_sel;
+    return;
+  }
+  const int plane = o.Ho * o.Wo;
+  img = m / plane;
+  int r = m - img * plane;
+  const int strip_px = o.block_h * o.Wo;                   // pixels of a full strip of block_h rows
+  const int strip = r / strip_px;
+  r -= strip * strip_px;
+  const int rows = min(o.block_h, o.Ho - strip * o.block_h);   // rows of this strip (the last one may be short)
+  const int block_px = rows * o.block_w;                   // pixels of a full-width block of this strip
+  const int block = r / block_px;
+  r -= block * block_px;
+  const int cols = min(o.block_w, o.Wo - block * o.block_w);   // columns of this block (the last one may be narrow)
+  const int y = r / cols;
+  pix = (strip * o.block_h + y) * o.Wo + block * o.block_w + (r - y * cols);
+}
+
 // Epilogue parameter table of one tile's output channels (BatchNorm calls only); padding columns get neutral values.
 __device__ __noinline__ void fill_epilogue_table(const DcnArgs &a, float *table, int pitch, int group, int n_tile, int tile_n) {
   const int cout_g = a.Cout / a.groups;
@@ -690,8 +727,14 @@ __global__ void __launch_bounds__(CtaShape<NARROW>::kThreads, CtaShape<NARROW>::
   const int m_tile = blockIdx.x, n_tile = blockIdx.y, group = blockIdx.z;
   const int m0 = m_tile * kTileM;
   const int plane_out = a.Ho * a.Wo;
-  const int plane_sel = (a.row_end - a.row_begin) * a.Wo;   // tile rows enumerate the selected output rows only
-  const int pix_first = a.row_begin * a.Wo;
+  PixelOrder order;
+  order.plane_sel = (a.row_end - a.row_begin) * a.Wo;        // tile rows enumerate the selected output rows only
+  order.pix_first = a.row_begin * a.Wo;
+  order.m_first = a.m_first;
+  order.block_h = u.block_h;
+  order.block_w = u.block_w;
+  order.Ho = a.Ho;
+  order.Wo = a.Wo;
   const int K = a.Kh * a.Kw;
   const int cin_g = a.Cin / a.groups, cin_dg = a.Cin / a.dgroups;
   const int k_blocks = u.k_blocks;
@@ -759,9 +802,7 @@ __global__ void __launch_bounds__(CtaShape<NARROW>::kThreads, CtaShape<NARROW>::
       RawTap t = {0.0f, 0.0f, 1.0f, -1, 0};
       const int m = m0 + row;
       if (m < u.m_total) {
-        const int f = a.m_first + m;
-        t.img = f / plane_sel;
-        t.pix = pix_first + f - t.img * plane_sel;
+        pixel_of(order, m, t.img, t.pix);
         if constexpr (!PLAIN) {
           const int n = a.n_begin + t.img;
           const int mch = dgi * K + kp;
@@ -973,8 +1014,8 @@ __global__ void __launch_bounds__(CtaShape<NARROW>::kThreads, CtaShape<NARROW>::
       const int quad = warp & 3;                  // TMEM lanes [32*quad, 32*quad+32)
       const int m = m0 + quad * 32 + lane;
       const bool row_ok = m < u.m_total;
-      const int img = row_ok ? (a.m_first + m) / plane_sel : 0;
-      const int pix = row_ok ? pix_first + (a.m_first + m) - img * plane_sel : 0;
+      int img = 0, pix = 0;
+      if (row_ok) pixel_of(order, m, img, pix);
       const int cout_g = a.Cout / a.groups;
       const int co_base = group * cout_g + n_tile * u.tile_n;
       const int tile_n = u.tile_n;
@@ -1147,6 +1188,12 @@ UmmaLaunch shape_umma_launch(const DcnArgs &a, const UmmaPlan &p, int sms, UmmaA
   u.m_tiles = p.m_tiles;
   u.m_total = (int)p.m_total;
   u.b_stage_bytes = (unsigned)p.b_stage_bytes;
+  // whole images (no row or pixel restriction): 8 x 16 pixel blocks along M
+  const bool whole = a.m_first == 0 && a.row_begin == 0 && a.row_end == a.Ho &&
+                     a.m_count == (long long)(a.n_end - a.n_begin) * a.Ho * a.Wo;
+  u.block_h = whole ? GACB_DCN_BLOCK_H : 0;
+  u.block_w = (whole && GACB_DCN_BLOCK_H) ? kTileM / (GACB_DCN_BLOCK_H ? GACB_DCN_BLOCK_H : 1) : 0;
+  if (!u.block_w) u.block_h = 0;
   // accumulator columns: tile_n, twice that with the cross-product accumulator; allocations are powers of two >= 32
   const int slab = (p.tile_n + 31) / 32 * 32;
   u.cross_col = slab;
