@@ -387,6 +387,35 @@ class ShardedMsda:
             self._replicate_entry(b)
             self.s_compute.wait_event(self._event(self.s_comm))
             self._compute_entry(b)
+        self.s_compute.wait_stream(self.s_comm)      # the step ends on the compute stream (and a capture can close)
+
+    def capture_resident(self):
+        """The device-resident step as ONE CUDA graph (collectives included), returned as a callable that replays
+        it on the compute stream.  A step is six collectives and six kernel launches issued from Python; at eight
+        GPUs each kernel is a few tens of microseconds, so launched one by one the step is paced by the host
+        (about 0.1 ms per batch entry), not by NVLink or the kernel.  Every rank must capture and replay in step.
+        Returns ``None`` when the capture fails (the caller keeps calling ``step_resident``)."""
+        if self.device.type != "cuda":
+            return None
+        torch = self.torch
+        try:
+            for _ in range(2):
+                self.step_resident()                 # warm: NCCL channels, kernel attributes
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=self.s_compute, capture_error_mode="thread_local"):
+                self.step_resident()
+            torch.cuda.synchronize(self.device)
+        except Exception:
+            torch.cuda.synchronize(self.device)
+            return None
+        self._resident_graph = graph
+
+        def replay():
+            with torch.cuda.stream(self.s_compute):
+                graph.replay()
+
+        return replay
 
     def step(self):
         """One end-to-end step from the pinned host buffers ``self.host[...]`` to ``self.host['output']``

@@ -454,6 +454,16 @@ def test_conv_offset_split_feeds_dcn(case, conv_small, dev):
     want = dcnv2_fused_c(c["X"], ref_conv[:, :18], ref_conv[:, 18:], w2, b2, relu=True, padding=(1, 1))
     # offsets that differ in the last bits move samples slightly: the chain is compared at the reduced gate
     assert_rel_gate(y.cpu().numpy(), want, 1e-3, f"{case} chain")
+    # ... and so that an error of the deformable kernel cannot hide behind that gate: the same second half with
+    # the ORACLE's offsets and scores fed to both sides, at the float32 gate
+    y2 = ops.dcnv2_forward(x, torch.from_numpy(np.ascontiguousarray(ref_conv[:, :18])).to(device),
+                           torch.from_numpy(np.ascontiguousarray(ref_conv[:, 18:])).to(device),
+                           torch.from_numpy(w2).to(device), torch.from_numpy(b2).to(device), padding=(1, 1),
+                           mask_is_logits=True, relu=True)
+    torch.cuda.synchronize()
+    assert_fp32_gate(y2.cpu().numpy(), want, f"{case} chain, oracle offsets")
+    # and the first half alone at the float32 gate
+    assert_fp32_gate(whole.cpu().numpy(), ref_conv, f"{case} conv_offset")
 
 
 @pytest.mark.parametrize("label,wl_args", [
