@@ -207,6 +207,99 @@ def nccl_high_priority_options():
     return opts
 
 
+class _DevicePointer:
+    """Lets torch view device memory that the library allocated (``__cuda_array_interface__``)."""
+
+    def __init__(self, ptr: int, shape, typestr: str) -> None:
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(ptr), False), "version": 2}
+
+
+class PeerBuffers:
+    """One device buffer per rank that every other rank of the node can read with copy-engine peer copies.
+
+    Each rank allocates ``nbytes`` through the library (``gacb_ipc_alloc``), the CUDA IPC handles travel over the
+    process group, every rank maps the others' buffers, and ``barrier(stream)`` enqueues the library's bounded
+    device-side barrier ("every rank's stream has got here").  ``pull(dst, rank, offset, nbytes, stream)`` is one
+    ``cudaMemcpyAsync`` from rank ``rank``'s buffer into this GPU's own memory: NVLink traffic without a kernel.
+    ``close()`` unmaps and frees; it is collective (ends with a barrier of the group)."""
+
+    def __init__(self, nbytes: int, device, group=None) -> None:
+        import ctypes
+
+        import torch
+        import torch.distributed as dist
+
+        from . import native
+
+        self.torch, self.dist, self.native, self.group = torch, dist, native, group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.device = torch.device(device)
+        self.nbytes = int(nbytes)
+        lib = native.load()
+        self._lib = lib
+        with torch.cuda.device(self.device):
+            mine = []
+            for size in (self.nbytes, 4096):              # payload, then flags (world uint32) + step counter
+                ptr, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+                native.check(lib.gacb_ipc_alloc(size, ctypes.byref(ptr), handle), "gacb_ipc_alloc")
+                mine.append((int(ptr.value), bytes(handle.raw)))
+            self.local_ptr, self.local_flags = mine[0][0], mine[1][0]
+            handles = [None] * self.world
+            dist.all_gather_object(handles, (mine[0][1], mine[1][1]), group=group)
+            self.ptrs, self.flag_ptrs, self._opened = [], [], []
+            for r, (payload, flags) in enumerate(handles):
+                if r == self.rank:
+                    self.ptrs.append(self.local_ptr)
+                    self.flag_ptrs.append(self.local_flags)
+                    continue
+                got = []
+                for handle in (payload, flags):
+                    ptr = ctypes.c_void_p()
+                    native.check(lib.gacb_ipc_open(handle, ctypes.byref(ptr)), "gacb_ipc_open")
+                    got.append(int(ptr.value))
+                    self._opened.append(int(ptr.value))
+                self.ptrs.append(got[0])
+                self.flag_ptrs.append(got[1])
+            self._flag_table = (ctypes.c_void_p * self.world)(*self.flag_ptrs)
+            self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        dist.barrier(group)
+
+    def local_tensor(self, shape, dtype):
+        """This rank's buffer as a torch tensor (no copy)."""
+        torch = self.torch
+        typestr = {torch.float32: "<f4", torch.bfloat16: "<i2", torch.uint8: "|u1"}[dtype]
+        t = torch.as_tensor(_DevicePointer(self.local_ptr, shape, typestr), device=self.device)
+        return t.view(torch.bfloat16) if dtype == torch.bfloat16 else t
+
+    def pull(self, dst, rank: int, offset: int, nbytes: int, stream) -> None:
+        if offset < 0 or offset + nbytes > self.nbytes or nbytes > dst.numel() * dst.element_size():
+            raise ValueError("peer copy outside the buffers")
+        rc = self._lib.gacb_copy_async(dst.data_ptr(), self.ptrs[rank] + offset, nbytes, int(stream.cuda_stream))
+        self.native.check(rc, "gacb_copy_async")
+
+    def barrier(self, stream) -> None:
+        rc = self._lib.gacb_peer_barrier(self._flag_table, self.local_flags, self.local_flags + 2048, self.world, self.rank,
+                                         self.status.data_ptr(), int(stream.cuda_stream))
+        self.native.check(rc, "gacb_peer_barrier")
+
+    def check(self) -> None:
+        """Raises ``BackendError`` if a device-side barrier gave up waiting for a peer."""
+        self.native.check(self._lib.gacb_status_from_word(int(self.status.item())), "peer barrier")
+
+    def close(self) -> None:
+        if self._lib is None:
+            return
+        self.torch.cuda.synchronize(self.device)
+        self.dist.barrier(self.group)                     # nobody still reads a buffer that is about to go away
+        for ptr in self._opened:
+            self._lib.gacb_ipc_close(ptr)
+        self.dist.barrier(self.group)
+        self._lib.gacb_ipc_free(self.local_ptr)
+        self._lib.gacb_ipc_free(self.local_flags)
+        self._lib = None
+
+
 class _NoStream:
     """Stand-in for streams and events on a CPU-only box: everything runs in program order."""
 
@@ -233,7 +326,10 @@ class ShardedMsda:
     so entry b+1 is on the wire while the kernel gathers from entry b.  The all-gather output is rank-major, i.e.
     the first S rows of the ``[world*Sp, H, D]`` buffer ARE the slab in order; the kernel reads only this GPU's
     own memory (no peer loads).  ``replicate="broadcast"`` instead has rank 0 hold the whole value and broadcast
-    slab after slab.  ``value_storage="bfloat16"`` casts the shard on the device before it travels, halving the
+    slab after slab.  ``replicate="peer_copy"`` (device-resident steps only) replaces the collective by copy-engine
+    peer copies out of IPC-mapped shard buffers (``PeerBuffers``): no SM is taken from the gather kernel, so the
+    copies of slab b+1 really run beside the kernel on slab b; two bounded device-side barriers per step order the
+    ranks.  ``value_storage="bfloat16"`` casts the shard on the device before it travels, halving the
     bytes on the wire; the kernel then reads bf16 texels and accumulates in float32.
 
     The reference runs one device (``src/gac/execution/cuda.py:132-138``): there is no behaviour to match beyond
@@ -251,8 +347,8 @@ class ShardedMsda:
         import torch
         import torch.distributed as dist
 
-        if replicate not in ("all_gather", "broadcast"):
-            raise ValueError("replicate must be 'all_gather' or 'broadcast'")
+        if replicate not in ("all_gather", "broadcast", "peer_copy"):
+            raise ValueError("replicate must be 'all_gather', 'broadcast' or 'peer_copy'")
         if value_storage not in ("float32", "bfloat16"):
             raise ValueError("value_storage must be 'float32' or 'bfloat16'")
         self.torch, self.dist, self.group = torch, dist, group
@@ -272,8 +368,23 @@ class ShardedMsda:
         cuda = self.device.type == "cuda"
         qc = self.q1 - self.q0
         dev = dict(device=self.device)
-        self.shard32 = torch.zeros((batch, self.rows, heads, head_dim), dtype=torch.float32, **dev)
-        self.shard = self.shard32 if self.storage == torch.float32 else torch.zeros_like(self.shard32, dtype=self.storage)
+        self.peers = None
+        if replicate == "peer_copy":
+            if not cuda or self.world == 1:
+                raise ValueError("replicate='peer_copy' needs CUDA devices and more than one rank")
+            # the shard every rank pulls from lives in a buffer the others can map; float32 shards are uploaded
+            # straight into it, bf16 shards are cast into it
+            item = 4 if self.storage == torch.float32 else 2
+            self.peers = PeerBuffers(batch * self.rows * heads * head_dim * item, self.device, group)
+            shared = self.peers.local_tensor((batch, self.rows, heads, head_dim), self.storage)
+        if self.peers is not None and self.storage == torch.float32:
+            self.shard32 = shared
+        else:
+            self.shard32 = torch.zeros((batch, self.rows, heads, head_dim), dtype=torch.float32, **dev)
+        if self.storage == torch.float32:
+            self.shard = self.shard32
+        else:
+            self.shard = shared if self.peers is not None else torch.zeros_like(self.shard32, dtype=self.storage)
         self.slabs = torch.zeros((batch, self.world * self.rows, heads, head_dim), dtype=self.storage, **dev)
         self.loc = torch.empty((batch, qc, heads, self.L, points, 2), dtype=torch.float32, **dev)
         self.attn = torch.empty((batch, qc, heads, self.L, points), dtype=torch.float32, **dev)
@@ -307,6 +418,12 @@ class ShardedMsda:
         item = 4 if self.storage == self.torch.float32 else 2
         slab = self.B * self.rows * self.H * self.D * item
         return slab * (self.world - 1)
+
+    def close(self) -> None:
+        """Collective: releases the peer-mapped buffers of ``replicate='peer_copy'`` (a no-op otherwise)."""
+        if self.peers is not None:
+            self.peers.close()
+            self.peers = None
 
     def load_host(self, value, locations, weights) -> None:
         """Fill the pinned staging buffers with this rank's share of full host arrays (test / bench set-up)."""
@@ -353,19 +470,41 @@ class ShardedMsda:
                 if self.world > 1:
                     dist.broadcast(self.slabs[b, : self.S], src=0, group=self.group)
                 return
-            if self.storage != torch.float32:
-                if self.device.type == "cuda":
-                    from . import native
-
-                    rc = native.load().gacb_cast_f32_to_bf16(self.shard32[b].data_ptr(), self.shard[b].data_ptr(),
-                                                             self.shard32[b].numel(), int(self.s_comm.cuda_stream))
-                    native.check(rc, "gacb_cast_f32_to_bf16")
-                else:
-                    self.shard[b].copy_(self.shard32[b])
+            if self.storage != torch.float32 and self.replicate != "peer_copy":
+                self._cast_entry(b)
+            if self.replicate == "peer_copy":
+                # pull every rank's rows of slab b with the copy engines, the neighbours first so that the ranks
+                # do not all read from the same GPU at once; this rank's own rows are a local copy
+                entry = self.shard[b].numel() * self.shard.element_size()
+                for k in range(self.world):
+                    r = (self.rank + k) % self.world
+                    self.peers.pull(self.slabs[b, r * self.rows:(r + 1) * self.rows], r, b * entry, entry, self.s_comm)
+                return
             if self.world > 1:
                 dist.all_gather_into_tensor(self.slabs[b], self.shard[b], group=self.group)
             else:
                 self.slabs[b].copy_(self.shard[b], non_blocking=True)
+
+    def _cast_entry(self, b: int) -> None:
+        """float32 shard b -> storage dtype (bf16), on the comm stream."""
+        if self.device.type == "cuda":
+            from . import native
+
+            rc = native.load().gacb_cast_f32_to_bf16(self.shard32[b].data_ptr(), self.shard[b].data_ptr(),
+                                                     self.shard32[b].numel(), int(self.s_comm.cuda_stream))
+            native.check(rc, "gacb_cast_f32_to_bf16")
+        else:
+            self.shard[b].copy_(self.shard32[b])
+
+    def _peer_prologue(self) -> None:
+        """peer_copy: before anybody pulls, every rank's shards of this step must be in place (and every pull of
+        the previous step done, before a cast overwrites a shard): two device-side barriers around the casts."""
+        with self._ctx(self.s_comm):
+            self.peers.barrier(self.s_comm)              # all pulls of the previous step have been enqueued and run
+            if self.storage != self.torch.float32:
+                for b in range(self.B):
+                    self._cast_entry(b)
+            self.peers.barrier(self.s_comm)              # all shards of this step are ready
 
     def _compute_entry(self, b: int) -> None:
         value = self.slabs[b, : self.S].unsqueeze(0)
@@ -383,6 +522,8 @@ class ShardedMsda:
         """One step with the shards (or, for ``broadcast``, rank 0's whole value) already on the device:
         replication of entry b+1 overlaps the kernel of entry b.  Returns after enqueueing."""
         self.s_comm.wait_stream(self.s_compute)      # the previous step's kernels still read the slabs
+        if self.replicate == "peer_copy":
+            self._peer_prologue()
         for b in range(self.B):
             self._replicate_entry(b)
             self.s_compute.wait_event(self._event(self.s_comm))
@@ -424,6 +565,9 @@ class ShardedMsda:
         self.s_h2d.wait_stream(self.s_comm)          # shard buffers are free once the previous gathers are done
         self.s_h2d.wait_stream(self.s_compute)
         self.s_comm.wait_stream(self.s_compute)
+        if self.replicate == "peer_copy":
+            raise NotImplementedError("the host-buffer step uses replicate='all_gather'; peer_copy is the "
+                                      "device-resident form (step_resident)")
         for b in range(self.B):
             with self._ctx(self.s_h2d):
                 self.shard32[b].copy_(h["value_shard"][b], non_blocking=True)

@@ -92,6 +92,12 @@ SIGNATURES = {
     "gacb_checked_violations": (_i, [ctypes.POINTER(ctypes.c_uint), ctypes.POINTER(ctypes.c_uint)]),
     "gacb_status_from_word": (_i, [ctypes.c_int32]),
     "gacb_read_status_word": (_i, [_vp, _vp]),
+    "gacb_ipc_alloc": (_i, [_sz, ctypes.POINTER(_vp), ctypes.c_char_p]),
+    "gacb_ipc_open": (_i, [ctypes.c_char_p, ctypes.POINTER(_vp)]),
+    "gacb_ipc_close": (_i, [_vp]),
+    "gacb_ipc_free": (_i, [_vp]),
+    "gacb_copy_async": (_i, [_vp, _vp, _sz, _vp]),
+    "gacb_peer_barrier": (_i, [ctypes.POINTER(_vp), _vp, _vp, _i, _i, _vp, _vp]),
     "gacb_cast_f32_to_bf16": (_i, [_vp, _vp, _sz, _vp]),
     "gacb_gather_probe": (_i, [_vp, _sz, _i, _i, _i, ctypes.c_uint32, _vp, ctypes.POINTER(_sz), _vp]),
 }

@@ -348,6 +348,30 @@ int gacb_checked_violations(unsigned int *count, unsigned int *last_site);
 int gacb_status_from_word(int32_t word);
 int gacb_read_status_word(const int32_t *status_word, void *stream);
 
+/* Peer-memory plumbing for the multi-GPU form (one process per GPU on one node).  No reference counterpart: GAC
+ * runs one device.  Query-sharded MSDA needs the whole value tensor in each GPU's own memory; these calls let the
+ * ranks bring a sharded value together with COPY-ENGINE peer copies over NVLink, which -- unlike a collective's
+ * kernels -- take no SM and run beside the gather kernel.  The MSDA kernels themselves only ever read local memory.
+ *   gacb_ipc_alloc    cudaMalloc `bytes` (zeroed) and export a CUDA IPC handle (GACB_IPC_HANDLE_BYTES bytes) for it
+ *   gacb_ipc_open     map a buffer another process exported (peer access is enabled on demand); the result is
+ *                     valid as a copy source or destination in this process
+ *   gacb_ipc_close    unmap what gacb_ipc_open returned;  gacb_ipc_free  release what gacb_ipc_alloc returned
+ *   gacb_copy_async   cudaMemcpyAsync between any two addresses mapped in this process, on `stream`
+ *   gacb_peer_barrier enqueue on `stream` a one-block kernel that tells every rank "this rank has got here" and
+ *                     waits until every rank has: peer_flags[r] = rank r's flag array (world uint32, mapped here;
+ *                     peer_flags[rank] = local_flags), local_step = one device uint32 the kernel increments (so a
+ *                     captured launch keeps working).  The wait is bounded (about half a second); when it runs out
+ *                     *status_word is set to 2 and the kernel returns.  All ranks must enqueue the same number of
+ *                     barriers.  world <= 16. */
+#define GACB_IPC_HANDLE_BYTES 64
+int gacb_ipc_alloc(size_t bytes, void **ptr, unsigned char *handle);
+int gacb_ipc_open(const unsigned char *handle, void **ptr);
+int gacb_ipc_close(void *ptr);
+int gacb_ipc_free(void *ptr);
+int gacb_copy_async(void *dst, const void *src, size_t bytes, void *stream);
+int gacb_peer_barrier(void *const *peer_flags, void *local_flags, void *local_step, int world, int rank,
+                      int32_t *status_word, void *stream);
+
 /* float32 -> bfloat16 (round to nearest even) for the bf16-storage value variant. */
 int gacb_cast_f32_to_bf16(const float *src, void *dst, size_t count, void *stream);
 
