@@ -69,9 +69,6 @@ constexpr int kMaxCoordRank = 8;
 #ifndef GACB_MSDA_UNROLL
 #define GACB_MSDA_UNROLL 4
 #endif
-#ifndef GACB_MSDA_FFMA2
-#define GACB_MSDA_FFMA2 0
-#endif
 constexpr int kRecordsPerThread = GACB_MSDA_RECORDS_PER_THREAD;   // phase-A budget: 20-byte tap records per thread of the CTA
 constexpr int kMaxRowsPerGroup = 8;
 constexpr int kCarveoutPercent = GACB_MSDA_CARVEOUT;  // shared-memory share of the 256 KB; the rest is L1
@@ -318,18 +315,10 @@ struct Tap<float, 4> {
   // Compiler fence on a loaded value: everything that uses it is scheduled after every load that precedes the fence.
   __device__ static __forceinline__ void pin(Raw &v) { asm volatile("" : "+f"(v.x), "+f"(v.y), "+f"(v.z), "+f"(v.w)); }
   __device__ static __forceinline__ void fma(float (&acc)[4], const Raw &v, float c) {
-#if GACB_MSDA_FFMA2
-    // two float32 FMAs per instruction (sm_100 FFMA2): each half is the same correctly rounded fmaf
-    const float2 cc = make_float2(c, c);
-    const float2 lo = __ffma2_rn(make_float2(v.x, v.y), cc, make_float2(acc[0], acc[1]));
-    const float2 hi = __ffma2_rn(make_float2(v.z, v.w), cc, make_float2(acc[2], acc[3]));
-    acc[0] = lo.x; acc[1] = lo.y; acc[2] = hi.x; acc[3] = hi.y;
-#else
     acc[0] = fmaf(v.x, c, acc[0]);
     acc[1] = fmaf(v.y, c, acc[1]);
     acc[2] = fmaf(v.z, c, acc[2]);
     acc[3] = fmaf(v.w, c, acc[3]);
-#endif
   }
 };
 
@@ -341,17 +330,6 @@ struct Tap<__nv_bfloat16, 8> {
   }
   __device__ static __forceinline__ void pin(Raw &v) { asm volatile("" : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)); }
   __device__ static __forceinline__ void fma(float (&acc)[8], const Raw &v, float c) {
-#if GACB_MSDA_FFMA2
-    const float2 cc = make_float2(c, c);
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const float2 r = __ffma2_rn(make_float2(bf16_lo(w[k]), bf16_hi(w[k])), cc, make_float2(acc[2 * k], acc[2 * k + 1]));
-      acc[2 * k] = r.x;
-      acc[2 * k + 1] = r.y;
-    }
-    return;
-#endif
     acc[0] = fmaf(bf16_lo(v.x), c, acc[0]);
     acc[1] = fmaf(bf16_hi(v.x), c, acc[1]);
     acc[2] = fmaf(bf16_lo(v.y), c, acc[2]);

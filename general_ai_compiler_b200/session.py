@@ -31,7 +31,7 @@ from .compiler import TARGET, VIEW_OPS, CudaProgram, KernelLaunch
 from .errors import BackendError, DeviceUnavailableError, ValidationError
 from .ops import FUSED_MSDA, conv_attrs, dcn_attrs
 from .profiler import Profiler
-from .validation import bind_inputs
+from .validation import bind_inputs, parallel_copy
 
 
 @dataclass
@@ -161,6 +161,12 @@ class CudaSession:
     def pinned_inputs(self) -> dict:
         """NumPy views of the pinned staging buffers (fill in place, then pass them to ``run``)."""
         return dict(self._pinned_np)
+
+    @staticmethod
+    def _fresh_copy(staged: np.ndarray) -> np.ndarray:
+        out = np.empty_like(staged)
+        parallel_copy(out, staged)
+        return out
 
     def _lookup(self, name: str):
         if name in self._inputs:
@@ -302,7 +308,7 @@ class CudaSession:
         for name, arr in bound.items():
             staged = self._pinned_np[name]
             if arr.ctypes.data != staged.ctypes.data:
-                np.copyto(staged, arr)
+                parallel_copy(staged, arr)
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         # everything queued earlier on the compute stream (a previous run reading these buffers) comes first
         self._h2d_stream.wait_stream(self._stream)
@@ -346,7 +352,7 @@ class CudaSession:
             if not instrument and self._can_overlap():
                 with torch.cuda.device(self._device):
                     gpu_ms = self._run_overlapped(bound)
-                    outputs = {name: (self._pinned_out[name].numpy().copy() if self._fresh_outputs
+                    outputs = {name: (self._fresh_copy(self._pinned_out[name].numpy()) if self._fresh_outputs
                                       else self._pinned_out[name].numpy())
                                for name in self.program.graph.outputs}
                 return RunResult(outputs, (time.perf_counter() - started) * 1000.0, gpu_ms, None, profiler)
@@ -358,7 +364,7 @@ class CudaSession:
                     for name, arr in bound.items():
                         staged = self._pinned_np[name]
                         if arr.ctypes.data != staged.ctypes.data:   # caller did not fill the pinned view in place
-                            np.copyto(staged, arr)
+                            parallel_copy(staged, arr)
                         self._inputs[name].copy_(self._pinned[name], non_blocking=True)
                 self._launch_all(profiler, instrument, event_pairs)
                 end.record(self._stream)
@@ -366,7 +372,7 @@ class CudaSession:
                     for name in self.program.graph.outputs:
                         self._pinned_out[name].copy_(self._lookup(name), non_blocking=True)
                     self._stream.synchronize()
-                    outputs = {name: (self._pinned_out[name].numpy().copy() if self._fresh_outputs
+                    outputs = {name: (self._fresh_copy(self._pinned_out[name].numpy()) if self._fresh_outputs
                                       else self._pinned_out[name].numpy())
                                for name in self.program.graph.outputs}
                 self._check_device_status()
@@ -392,7 +398,7 @@ class CudaSession:
         torch = self._torch
         with self._lock, torch.cuda.device(self._device), torch.cuda.stream(self._stream):
             for name, arr in bound.items():
-                np.copyto(self._pinned_np[name], arr)
+                parallel_copy(self._pinned_np[name], arr)
                 self._inputs[name].copy_(self._pinned[name], non_blocking=True)
             self._stream.synchronize()
 

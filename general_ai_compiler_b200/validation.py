@@ -20,6 +20,43 @@ from .errors import ValidationError
 from .ir import Graph
 
 
+_CHUNK_BYTES = 8 << 20     # arrays above this size are checked / copied in pieces by a few host threads
+_pool = None
+
+
+def host_pool():
+    """A small thread pool for the host-side passes over large inputs (NumPy drops the GIL inside them)."""
+    global _pool
+    if _pool is None:
+        import os
+        from concurrent.futures import ThreadPoolExecutor
+
+        cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+        _pool = ThreadPoolExecutor(max_workers=max(1, min(16, cores)))
+    return _pool
+
+
+def _pieces(arr: np.ndarray):
+    flat = arr.reshape(-1)
+    step = max(1, _CHUNK_BYTES // max(1, arr.itemsize))
+    return [flat[i:i + step] for i in range(0, flat.size, step)]
+
+
+def all_finite(arr: np.ndarray) -> bool:
+    """``np.all(np.isfinite(arr))`` for a C-contiguous array, in pieces over the host pool when it is large."""
+    if arr.nbytes <= 2 * _CHUNK_BYTES:
+        return bool(np.all(np.isfinite(arr)))
+    return all(host_pool().map(lambda piece: bool(np.isfinite(piece).all()), _pieces(arr)))
+
+
+def parallel_copy(dst: np.ndarray, src: np.ndarray) -> None:
+    """``np.copyto(dst, src)`` for same-shape C-contiguous arrays, in pieces over the host pool when they are large."""
+    if src.nbytes <= 2 * _CHUNK_BYTES or not (dst.flags.c_contiguous and src.flags.c_contiguous):
+        np.copyto(dst, src)
+        return
+    list(host_pool().map(lambda pair: np.copyto(pair[0], pair[1]), zip(_pieces(dst), _pieces(src))))
+
+
 def bind_inputs(graph: Graph, inputs: Mapping[str, np.ndarray], *, check_finite: bool = True) -> dict:
     """Exact names, shapes, dtypes, C-contiguity and finiteness; nothing is copied."""
     if set(inputs) != set(graph.inputs):
@@ -32,7 +69,7 @@ def bind_inputs(graph: Graph, inputs: Mapping[str, np.ndarray], *, check_finite:
                 f"input {name!r} requires {spec.shape}/{spec.dtype}, got {arr.shape}/{arr.dtype}")
         if not arr.flags.c_contiguous:
             raise ValidationError(f"input {name!r} must be C-contiguous")
-        if check_finite and not np.all(np.isfinite(arr)):
+        if check_finite and not all_finite(arr):
             raise ValidationError(f"input {name!r} must contain finite values")
         bound[name] = arr
     return bound

@@ -294,8 +294,10 @@ int gacb_dcnv2_workspace_parts(int n, int Cin, int H, int W, int Cout, int Kh, i
  *   - a call whose scratch need (gacb_dcnv2_workspace_bytes for n_end - n_begin images) exceeds the built-in size
  *     is rejected with GACB_ERR_UNSUPPORTED before anything is launched; split the images over several calls.
  *     BEVFormer-base's stage shapes fit with all six cameras (38.0 MB and 27.3 MB);
- *   - the first call on each device looks up the array's device address (with that device current) and keeps it;
- *     make that first call before any stream capture;
+ *   - the first call on each device looks up the array's device address (with that device current) and keeps it
+ *     for the life of the process: make that first call before any stream capture, have the device that owns
+ *     `stream` current at every call (the address is looked up for the CURRENT device), and do not reset the device
+ *     or destroy its primary context between calls (the remembered address would then be stale);
  *   - all calls on a device share the one array and it keeps whatever the last call left.  Nothing in it has to
  *     be zero beforehand (every byte a call reads is written by that call first), but two calls that overlap in
  *     time on the same GPU -- different streams, or different host threads -- race on it: serialise them. */
