@@ -703,6 +703,9 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=120.0,
                     help="--impl reference: CPU time the whole run may take; each step is a sample sized to fit it")
+    ap.add_argument("--msda-tile-path", action="store_true",
+                    help="let one-level raster-query workloads (base_tsa, tiny_tsa) run the shared-memory tile kernel "
+                         "(gacb_msda_tile_path(1)); the profiling case for msda_tile_kernel")
     ap.add_argument("--kernel-only", action="store_true",
                     help="device-resident launches only (no host-buffer loop, no CPU baseline): the profiling case")
     args = ap.parse_args()
@@ -753,6 +756,8 @@ def main() -> None:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
     device = ops.require_device(local_rank)
     torch.cuda.set_device(device)
+    if args.msda_tile_path:
+        ops.native.load().gacb_msda_tile_path(1)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device, pg_options=nccl_high_priority_options())
