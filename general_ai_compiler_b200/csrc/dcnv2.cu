@@ -50,6 +50,7 @@
 //    flag, sets the caller's status word, drains what it issued, frees TMEM and
 //    returns.
 #include <algorithm>
+#include <atomic>
 #include <mutex>
 #include <type_traits>
 
@@ -478,6 +479,21 @@ __device__ __forceinline__ bool mbar_wait2(uint32_t bar0, uint32_t parity0, uint
   }
   *abort_flag = 1;
   return false;
+}
+// Bounded wait for a whole warp: lane 0 polls (pausing between polls, so that idle roles leave the shared-memory
+// pipe to the tensor core's operand reads) and the outcome is broadcast.  All lanes must call it.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag, int lane) {
+  int ok = 0;
+  if (lane == 0) {
+    ok = -1;
+    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+      if (mbar_try_wait(bar, parity)) { ok = 1; break; }
+      if (*abort_flag) { ok = 0; break; }
+      __nanosleep(40);
+    }
+    if (ok < 0) { *abort_flag = 1; ok = 0; }
+  }
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -1170,6 +1186,406 @@ __global__ void __launch_bounds__(CtaShape<NARROW>::kThreads, CtaShape<NARROW>::
   }
 }
 
+// ----------------------------------------------------------------------------------------------
+// Plain convolution with few output channels (the 27-channel conv_offset) from a staged input window
+// ----------------------------------------------------------------------------------------------
+// A plain stride-1 convolution gathers nothing: the A operand of kernel point (ky, kx) is the input window shifted
+// by (ky, kx).  A persistent CTA therefore stages, per 16 x 8 pixel tile and per group of 64 or 128 input channels,
+// the (16 + Kh - 1) x (8 + Kw - 1) window of the channel-last bf16 copy ONCE in shared memory, in the tensor core's
+// un-swizzled K-major layout [8-channel chunk][texel][8 channels] (a core matrix = eight consecutive texels of a
+// window row x 16 bytes), and issues one tcgen05.mma per (kernel point, 16 channels) whose A descriptor simply
+// starts (ky * window width + kx) texels further on: the eight pixels of a tile row are eight consecutive texels
+// (16 bytes apart), the next tile row is one window row further (the descriptor's stride byte offset), the next
+// 8-channel chunk one chunk stride further (its leading byte offset).  There are no producer warps and no A ring:
+// eight warps copy the next windows with 16-byte cp.async while the tensor core works on the current one, one
+// thread streams the packed weights of a few kernel points at a time through a ring, four warps store finished
+// accumulators.  Taps outside the image are zero texels of the window.
+//
+// With 32 output columns an MMA is a few cycles of tensor work, but a thread issues one only every ~100 cycles,
+// whatever its shape (measured: the same with N = 16 or M = 64, and with independent accumulators).  So kWinAccs
+// threads issue side by side, each the 16-channel slices k ≡ j (mod kWinAccs) of every kernel point into its own
+// accumulator (a partial sum); the epilogue adds the partial sums.  Two such sets sit in tensor memory, so that a
+// tile's stores overlap the next tile's products.
+//
+// BF16 mode only (operands rounded to bf16, float32 accumulation), whole images, groups = 1, stride = dilation = 1,
+// at most 64 output channels, bias and ReLU only.
+constexpr int kWinTileH = 16, kWinTileW = 8;          // pixels of a tile: 16 rows x 8 columns = 128 MMA rows
+constexpr int kWinFillWarps = 8, kWinEpiWarps = 4;
+constexpr int kWinAccs = 4;                           // accumulators per tile = issuing threads (one warp each)
+constexpr int kWinLoaderWarp = kWinEpiWarps, kWinMmaWarp = kWinEpiWarps + 1, kWinFirstFillWarp = kWinMmaWarp + kWinAccs;
+constexpr int kWinThreads = (kWinEpiWarps + 1 + kWinAccs + kWinFillWarps) * 32;
+constexpr int kWinMaxBufs = 4, kWinMaxBStages = 8;    // sizes of the barrier arrays
+constexpr int kWinStageBytes = 24 * 1024;             // target size of one weight stage
+static_assert(kWinTileH * kWinTileW == kTileM, "a tile is one 128-row MMA");
+
+struct ConvWinArgs {
+  DcnArgs d;
+  const __nv_bfloat16 *xt;      // channel-last bf16 copy of images [n_begin, n_end)
+  const unsigned char *blob;    // packed weights: [channel group][kernel point][8-channel chunk][n_pad rows][8]
+  int32_t *status;
+  int n_pad;                    // MMA N: output channels rounded up to 32
+  int tiles_x, tiles_y, tiles_total;
+  int cgroups, cg_channels;     // channel groups per tile and channels per group (64 or 128)
+  int win_h, win_w, win_texels;
+  int chunk_stride;             // bytes between the 8-channel chunks of a window: an odd number of 16-byte units, so
+                                // that the fill's 16 lanes of one texel (one per chunk) spread over all banks
+  int stage_kps, cg_stages;     // kernel points per weight stage; stages per channel group
+  int win_bufs, b_stages;       // ring depths
+  unsigned win_bytes, kp_bytes, b_stage_bytes;
+  int tmem_cols;
+  int drop_weight_copies;       // test build only (GACB_DCN_FAULT_INJECT): the loader skips every copy
+};
+
+// Un-swizzled K-major operand: core matrices of 8 rows x 16 bytes, `lbo` bytes between the two core matrices an MMA
+// reads along K, `sbo` bytes between 8-row groups.
+__device__ __forceinline__ uint64_t umma_smem_desc_plain(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;                              // descriptor version of sm_100; layout type 0 = no swizzle
+  return d;
+}
+
+__global__ void __launch_bounds__(256) conv_window_pack_weights(const float *__restrict__ w, unsigned char *__restrict__ blob,
+                                                               int Cout, int Cin, int K, int n_pad, int cg_channels) {
+  const long long total = (long long)n_pad * Cin * K;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int ci = (int)(i % Cin);
+  const int kp = (int)((i / Cin) % K);
+  const int n = (int)(i / ((long long)Cin * K));
+  const float v = n < Cout ? __ldg(w + ((long long)n * Cin + ci) * K + kp) : 0.0f;
+  const int cg = ci / cg_channels, cc = ci - cg * cg_channels;
+  const size_t per_kp = (size_t)(cg_channels / 8) * n_pad * 16;
+  const size_t byte = ((size_t)cg * K + kp) * per_kp + ((size_t)(cc >> 3) * n_pad + n) * 16 + (cc & 7) * 2;
+  *reinterpret_cast<__nv_bfloat16 *>(blob + byte) = __float2bfloat16_rn(v);
+}
+
+__global__ void __launch_bounds__(kWinThreads, 1) conv_window_kernel(const __grid_constant__ ConvWinArgs u) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~(uintptr_t)127);
+  const DcnArgs &a = u.d;
+  unsigned char *windows = smem;
+  unsigned char *b_ring = smem + (size_t)u.win_bufs * u.win_bytes;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(b_ring + (size_t)u.b_stages * u.b_stage_bytes);
+  // bars: win_full[] | win_empty[] | b_full[] | b_empty[] | acc_full[2] | acc_empty[2] | drain[kWinAccs]
+  constexpr int kBars = 2 * kWinMaxBufs + 2 * kWinMaxBStages + 4 + kWinAccs;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + kBars);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  float *bias_s = reinterpret_cast<float *>(tmem_slot + 4);       // n_pad floats (zeros without a bias)
+  const uint32_t bar_base = smem_u32(bars);
+  auto win_full = [&](int b) { return bar_base + 8u * b; };
+  auto win_empty = [&](int b) { return bar_base + 8u * (kWinMaxBufs + b); };
+  auto b_full = [&](int s) { return bar_base + 8u * (2 * kWinMaxBufs + s); };
+  auto b_empty = [&](int s) { return bar_base + 8u * (2 * kWinMaxBufs + kWinMaxBStages + s); };
+  auto acc_full = [&](int s) { return bar_base + 8u * (2 * kWinMaxBufs + 2 * kWinMaxBStages + s); };
+  auto acc_empty = [&](int s) { return bar_base + 8u * (2 * kWinMaxBufs + 2 * kWinMaxBStages + 2 + s); };
+  auto drain = [&](int j) { return bar_base + 8u * (2 * kWinMaxBufs + 2 * kWinMaxBStages + 4 + j); };
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int K = a.Kh * a.Kw;
+  const int plane_out = a.Ho * a.Wo;
+  const int tiles_per_image = u.tiles_x * u.tiles_y;
+  if (tid == 0) {
+    for (int i = 0; i < kWinMaxBufs; ++i) {
+      mbar_init(win_full(i), kWinFillWarps);
+      mbar_init(win_empty(i), kWinAccs);      // one commit per issuing thread
+    }
+    for (int i = 0; i < kWinMaxBStages; ++i) {
+      mbar_init(b_full(i), 1);
+      mbar_init(b_empty(i), kWinAccs);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(acc_full(i), kWinAccs);
+      mbar_init(acc_empty(i), kWinEpiWarps);
+    }
+    for (int i = 0; i < kWinAccs; ++i) mbar_init(drain(i), 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (tid < u.n_pad) bias_s[tid] = (a.bias != nullptr && tid < a.Cout) ? __ldg(a.bias + tid) : 0.0f;
+  if (warp == kWinMmaWarp) tmem_alloc(smem_u32(tmem_slot), (uint32_t)u.tmem_cols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int set_cols = kWinAccs * u.n_pad;      // tensor-memory columns of one tile's accumulators
+
+  if (warp >= kWinFirstFillWarp) {
+    // ------------------------------------------------------------------ window fill (eight warps)
+    // A thread copies the 16-byte pieces (texel, chunk) with chunk = ft % chunks (neighbouring lanes read one texel's
+    // channels) and texel = ft / chunks, + 256 / chunks, ...; chunks is 8 or 16, so nothing below divides.
+    const int ft = tid - kWinFirstFillWarp * 32;                    // 0 .. 255
+    const int chunks = u.cg_channels / 8, chunk_shift = chunks == 16 ? 4 : 3;
+    const int c = ft & (chunks - 1), tt0 = ft >> chunk_shift, tt_step = (kWinFillWarps * 32) >> chunk_shift;
+    const int wy0 = tt0 / u.win_w, wx0 = tt0 - wy0 * u.win_w;
+    bool alive = true;
+    int buf = 0, round = 0;                                         // ring position: step % win_bufs, step / win_bufs
+    for (int t = blockIdx.x; t < u.tiles_total; t += gridDim.x) {
+      const int img = t / tiles_per_image, r = t - img * tiles_per_image;
+      const int ty = r / u.tiles_x, tx = r - ty * u.tiles_x;
+      const int y0 = ty * kWinTileH - a.ph, x0 = tx * kWinTileW - a.pw;     // input position of window texel (0, 0)
+      const __nv_bfloat16 *image = u.xt + (size_t)img * a.H * a.W * a.Cin;
+      for (int cg = 0; cg < u.cgroups; ++cg) {
+        if (alive) alive = mbar_wait_warp(win_empty(buf), (round & 1) ^ 1, abort_flag, lane);
+        if (alive) {
+          unsigned char *win = windows + (size_t)buf * u.win_bytes;
+          unsigned char *dst = win + (size_t)c * u.chunk_stride + (size_t)tt0 * 16;
+          const __nv_bfloat16 *src = image + cg * u.cg_channels + c * 8;
+          int wy = wy0, wx = wx0;
+          for (int tt = tt0; tt < u.win_texels; tt += tt_step, dst += tt_step * 16) {
+            const int gy = y0 + wy, gx = x0 + wx;
+            if (gy >= 0 && gy < a.H && gx >= 0 && gx < a.W) {
+              const int e = (int)GACB_INDEX((gy * a.W + gx) * a.Cin, (long long)a.H * a.W * a.Cin, 12);
+              async_copy_16(smem_u32(dst), src + e);
+            } else {
+              *reinterpret_cast<uint4 *>(dst) = make_uint4(0u, 0u, 0u, 0u);   // zero padding
+            }
+            wx += tt_step;
+            while (wx >= u.win_w) { wx -= u.win_w; ++wy; }
+          }
+          async_copy_commit();
+          async_copy_wait_all();
+          fence_proxy_async_smem();      // generic-proxy writes -> visible to the tensor core's async proxy
+        }
+        // one arrival per warp, after every lane's writes are fenced
+        const bool warp_alive = __all_sync(0xffffffffu, alive);
+        if (warp_alive && lane == 0) mbar_arrive(win_full(buf));
+        if (++buf == u.win_bufs) { buf = 0; ++round; }
+      }
+    }
+  } else if (warp == kWinLoaderWarp) {
+    // ------------------------------------------------------------------ weight loader (one lane)
+    if (lane == 0) {
+      int s = 0, round = 0, issued = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < u.tiles_total && ok; t += gridDim.x)
+        for (int cg = 0; cg < u.cgroups && ok; ++cg)
+          for (int k0 = 0; k0 < K; k0 += u.stage_kps) {
+            if (!mbar_wait(b_empty(s), (round & 1) ^ 1, abort_flag)) { ok = false; break; }
+            const uint32_t bytes = (uint32_t)min(u.stage_kps, K - k0) * u.kp_bytes;
+            mbar_arrive_expect_tx(b_full(s), bytes);
+            if (!(GACB_DCN_FAULT_INJECT && u.drop_weight_copies)) {
+              bulk_copy_g2s(smem_u32(b_ring + (size_t)s * u.b_stage_bytes), u.blob + ((size_t)cg * K + k0) * u.kp_bytes,
+                            bytes, b_full(s));
+              ++issued;
+            }
+            if (++s == u.b_stages) { s = 0; ++round; }
+          }
+      if (*abort_flag && issued > 0) {
+        // drain: every copy issued must have landed before shared memory is released.  Stage s, round `round` is the
+        // next one that would have been issued; the b_stages before it may still be in flight.
+        for (int back = 1; back <= u.b_stages && back <= issued; ++back) {
+          int ps = s - back, pr = round;
+          if (ps < 0) { ps += u.b_stages; --pr; }
+          for (uint32_t poll = 0; poll < kSpinLimit && !mbar_try_wait(b_full(ps), pr & 1); ++poll) {
+          }
+        }
+      }
+    }
+  } else if (warp >= kWinMmaWarp) {
+    // ------------------------------------------------------------------ MMA issuers (one lane of each of kWinAccs warps)
+    if (lane == 0) {
+      const int issuer = warp - kWinMmaWarp;          // takes the 16-channel slices issuer, issuer + kWinAccs, ...
+      const uint32_t idesc = umma_idesc(1, kTileM, u.n_pad);
+      const uint32_t a_lbo = (uint32_t)u.chunk_stride, a_sbo = (uint32_t)u.win_w * 16u;
+      const uint32_t b_lbo = (uint32_t)u.n_pad * 16u, b_sbo = 128u;
+      // descriptors with a zero start address; a start address is added in 16-byte units
+      const uint64_t a_desc0 = umma_smem_desc_plain(0, a_lbo, a_sbo), b_desc0 = umma_smem_desc_plain(0, b_lbo, b_sbo);
+      const uint32_t a_k16 = (2u * a_lbo) >> 4, b_k16 = (2u * b_lbo) >> 4;     // one 16-channel slice, in 16-byte units
+      const int k16_quads = u.cg_channels / (16 * kWinAccs);
+      bool ok = true;
+      int buf = 0, wround = 0, s = 0, bround = 0, it = 0;
+      for (int t = blockIdx.x; t < u.tiles_total && ok; t += gridDim.x, ++it) {
+        const int set = it & 1, use = it >> 1;
+        ok = mbar_wait(acc_empty(set), (use & 1) ^ 1, abort_flag);    // the epilogue has read this set's last tile
+        const uint32_t acc = tmem_base + (uint32_t)(set * set_cols + issuer * u.n_pad);
+        uint32_t accumulate = 0;                                      // 0 for the first MMA into the accumulator
+        for (int cg = 0; cg < u.cgroups && ok; ++cg) {
+          ok = mbar_wait(win_full(buf), wround & 1, abort_flag);
+          const uint32_t win = smem_u32(windows + (size_t)buf * u.win_bytes);
+          int ky = 0, kx = 0;
+          for (int k0 = 0; k0 < K && ok; k0 += u.stage_kps) {
+            ok = mbar_wait(b_full(s), bround & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const int k1 = min(K, k0 + u.stage_kps);
+            uint64_t bd = b_desc0 + (uint64_t)(smem_u32(b_ring + (size_t)s * u.b_stage_bytes) >> 4) + issuer * b_k16;
+            for (int kp = k0; kp < k1; ++kp) {
+              uint64_t ad = a_desc0 + (uint64_t)((win + (uint32_t)(ky * u.win_w + kx) * 16u) >> 4) + issuer * a_k16;
+              for (int q = 0; q < k16_quads; ++q) {
+                umma_ss<false>(acc, ad, bd, idesc, accumulate);
+                accumulate = 1u;
+                ad += kWinAccs * a_k16;
+                bd += kWinAccs * b_k16;
+              }
+              if (++kx == a.Kw) { kx = 0; ++ky; }
+            }
+            umma_commit(b_empty(s));       // the stage is free once these MMAs have read it
+            if (++s == u.b_stages) { s = 0; ++bround; }
+          }
+          if (ok) umma_commit(win_empty(buf));
+          if (++buf == u.win_bufs) { buf = 0; ++wround; }
+        }
+        if (ok) umma_commit(acc_full(set));
+      }
+      if (!ok) {
+        // after an abort: everything this thread issued must have retired before shared and tensor memory are released
+        umma_commit(drain(issuer));
+        for (uint32_t poll = 0; poll < kSpinLimit && !mbar_try_wait(drain(issuer), 0); ++poll) {
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (four warps, one per TMEM lane quadrant)
+    const int quad = warp & 3;
+    const int m = quad * 32 + lane;                 // tile row: pixel (m / 8, m % 8) of the tile
+    const int split_at = a.y_split != nullptr ? a.split_at : a.Cout;      // channels below it go to y
+    const bool relu = a.relu != 0;
+    int it = 0;
+    for (int t = blockIdx.x; t < u.tiles_total; t += gridDim.x, ++it) {
+      const int set = it & 1, use = it >> 1;
+      const bool go = mbar_wait_warp(acc_full(set), use & 1, abort_flag, lane);   // tcgen05.ld is warp-collective
+      if (!go) break;
+      tc_fence_after();
+      const int img = t / tiles_per_image, r = t - img * tiles_per_image;
+      const int ty = r / u.tiles_x, tx = r - ty * u.tiles_x;
+      const int oy = ty * kWinTileH + (m >> 3), ox = tx * kWinTileW + (m & 7);
+      const bool row_ok = oy < a.Ho && ox < a.Wo;
+      const int n_img = a.n_begin + img;
+      const int pix = oy * a.Wo + ox;
+      float *const y_lo = a.y + (long long)n_img * split_at * plane_out + pix;
+      float *const y_hi = a.y_split != nullptr
+                              ? a.y_split + ((long long)n_img * (a.Cout - split_at) - split_at) * plane_out + pix
+                              : nullptr;
+      const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(set * set_cols);
+      for (int col = 0; col < u.n_pad; col += 32) {
+        // the tile's value is the sum of its kWinAccs partial accumulators
+        uint32_t rr[32], xa[32];
+        tmem_ld32(lane_base + (uint32_t)col, rr);
+        tmem_ld32(lane_base + (uint32_t)(u.n_pad + col), xa);
+        tmem_ld_wait();
+#pragma unroll
+        for (int p = 2; p < kWinAccs; ++p) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) rr[j] = __float_as_uint(__fadd_rn(__uint_as_float(rr[j]), __uint_as_float(xa[j])));
+          tmem_ld32(lane_base + (uint32_t)(p * u.n_pad + col), xa);
+          tmem_ld_wait();
+        }
+        if (col + 32 >= u.n_pad) {
+          // everything of this tile has been read: the issuing thread may start the tile after next in this set
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acc_empty(set));
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) rr[j] = __float_as_uint(__fadd_rn(__uint_as_float(rr[j]), __uint_as_float(xa[j])));
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int co = col + j;
+            if (co < a.Cout) {
+              float v = __fadd_rn(__uint_as_float(rr[j]), bias_s[co]);
+              if (relu) v = fmaxf(v, 0.0f);
+              float *dst = (co < split_at ? y_lo : y_hi) + (long long)co * plane_out;
+#if GACB_CHECKED
+              const long long rel = co < split_at ? dst - a.y : dst - a.y_split;
+              const long long lim = (long long)a.N * (co < split_at ? split_at : a.Cout - split_at) * plane_out;
+              if (GACB_INDEX(rel, lim, 14) != rel) continue;
+#endif
+              __stcs(dst, v);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  __syncthreads();
+  if (tid == 0 && *abort_flag && u.status) atomicExch(u.status, 1);
+  if (warp == kWinMmaWarp) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, (uint32_t)u.tmem_cols);
+  }
+}
+
+// 0 = plain convolutions always take the gather kernel; 1 (default) = the window kernel where it applies.
+std::atomic<int> g_conv_window_path{1};
+
+// Does the window kernel apply, and with which shape?  (BF16 mode, plain convolution over whole images.)
+bool plan_conv_window(const DcnArgs &a, int mode, size_t blob_capacity, ConvWinArgs &u, size_t &smem) {
+  if (!g_conv_window_path.load(std::memory_order_relaxed)) return false;
+  const bool whole = a.m_first == 0 && a.row_begin == 0 && a.row_end == a.Ho &&
+                     a.m_count == (long long)(a.n_end - a.n_begin) * a.Ho * a.Wo;
+  if (mode != MODE_BF16 || a.offset != nullptr || !whole || a.bn_scale != nullptr) return false;
+  if (a.groups != 1 || a.sh != 1 || a.sw != 1 || a.dh != 1 || a.dw != 1) return false;
+  if (a.Cout > 64 || a.Cin % 64 || a.Kh * a.Kw > 49) return false;
+  if ((long long)(a.n_end - a.n_begin) * a.H * a.W * a.Cin > 2147483647LL) return false;
+  const int K = a.Kh * a.Kw;
+  u.n_pad = (a.Cout + 31) / 32 * 32;
+  u.cg_channels = a.Cin % 128 == 0 ? 128 : 64;
+  u.cgroups = a.Cin / u.cg_channels;
+  u.win_h = kWinTileH + a.Kh - 1;
+  u.win_w = kWinTileW + a.Kw - 1;
+  u.win_texels = u.win_h * u.win_w;
+  u.chunk_stride = (u.win_texels | 1) * 16;
+  u.win_bytes = (unsigned)(((size_t)(u.cg_channels / 8) * u.chunk_stride + 127) / 128 * 128);
+  u.kp_bytes = (unsigned)((size_t)(u.cg_channels / 8) * u.n_pad * 16);
+  u.stage_kps = std::max(1, std::min(K, kWinStageBytes / (int)u.kp_bytes));
+  u.cg_stages = (K + u.stage_kps - 1) / u.stage_kps;
+  u.b_stage_bytes = (unsigned)u.stage_kps * u.kp_bytes;
+  if ((size_t)u.cgroups * K * u.kp_bytes > blob_capacity) return false;
+  // the un-swizzled descriptor's offsets are 14-bit counts of 16 bytes
+  if ((size_t)u.chunk_stride >= (1u << 18) || (size_t)u.n_pad * 16 >= (1u << 18)) return false;
+  const size_t fixed = 128 /*alignment*/ + (2 * kWinMaxBufs + 2 * kWinMaxBStages + 4 + kWinAccs) * 8 + 16 + 64 * sizeof(float);
+  const size_t budget = 227 * 1024;
+  u.win_bufs = 3;
+  while (u.win_bufs > 2 && fixed + (size_t)u.win_bufs * u.win_bytes + 3 * (size_t)u.b_stage_bytes > budget) --u.win_bufs;
+  if (fixed + (size_t)u.win_bufs * u.win_bytes + 2 * (size_t)u.b_stage_bytes > budget) return false;
+  const size_t left = budget - fixed - (size_t)u.win_bufs * u.win_bytes;
+  u.b_stages = (int)std::min<size_t>(kWinMaxBStages, left / u.b_stage_bytes);
+  smem = fixed + (size_t)u.win_bufs * u.win_bytes + (size_t)u.b_stages * u.b_stage_bytes;
+  u.tiles_x = (a.Wo + kWinTileW - 1) / kWinTileW;
+  u.tiles_y = (a.Ho + kWinTileH - 1) / kWinTileH;
+  u.tiles_total = (a.n_end - a.n_begin) * u.tiles_x * u.tiles_y;
+  int cols = 32;
+  while (cols < 2 * kWinAccs * u.n_pad) cols <<= 1;
+  u.tmem_cols = cols;      // at most 2 * 4 * 64 = 512 columns
+  return true;
+}
+
+int launch_conv_window(const DcnArgs &a, ConvWinArgs &u, size_t smem, const __nv_bfloat16 *xt, unsigned char *blob,
+                       int32_t *status, cudaStream_t stream, int reuse_flags, int sms, int device) {
+  const int K = a.Kh * a.Kw;
+  if (!(reuse_flags & GACB_DCN_REUSE_WEIGHTS)) {
+    const long long welems = (long long)u.n_pad * a.Cin * K;
+    conv_window_pack_weights<<<(int)((welems + 255) / 256), 256, 0, stream>>>(a.w, blob, a.Cout, a.Cin, K, u.n_pad, u.cg_channels);
+    const int rc = check_cuda(cudaGetLastError(), "conv_window_pack_weights launch");
+    if (rc != GACB_OK) return rc;
+  }
+  u.d = a;
+  u.xt = xt;
+  u.blob = blob;
+  u.status = status;
+  u.drop_weight_copies = (reuse_flags & kTestDropWeightCopies) ? 1 : 0;
+  static std::mutex attr_lock;
+  static bool attr_done[64] = {};
+  {
+    std::lock_guard<std::mutex> guard(attr_lock);
+    if (!attr_done[device]) {
+      const int rc = check_cuda(cudaFuncSetAttribute(conv_window_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024),
+                                "cudaFuncSetAttribute(conv_window_kernel)");
+      if (rc != GACB_OK) return rc;
+      attr_done[device] = true;
+    }
+  }
+  const int grid = std::min(u.tiles_total, sms);
+  conv_window_kernel<<<grid, kWinThreads, smem, stream>>>(u);
+  return check_cuda(cudaGetLastError(), "conv_window_kernel launch");
+}
+
 // What launch_umma launches for a problem on a GPU with `sms` multiprocessors; fills the tiling fields of `u`.
 struct UmmaLaunch {
   bool narrow;
@@ -1250,6 +1666,20 @@ int launch_umma(const DcnArgs &a, const UmmaPlan &p, void *workspace, int32_t *s
   }
   int rc = check_cuda(cudaGetLastError(), "dcn_nhwc_kernel launch");
   if (rc != GACB_OK) return rc;
+  int sms = 148, device = 0;
+  rc = check_cuda(cudaGetDevice(&device), "cudaGetDevice");
+  if (rc != GACB_OK) return rc;
+  rc = check_cuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device), "cudaDeviceGetAttribute(SM count)");
+  if (rc != GACB_OK) return rc;
+  if (device < 0 || device >= 64) return fail(GACB_ERR_UNSUPPORTED, "dcnv2: device ordinal %d is out of range", device);
+  if constexpr (MODE == MODE_BF16) {
+    // a plain convolution with few output channels reads shifted windows instead of gathering (its own weight layout)
+    ConvWinArgs cw{};
+    size_t cw_smem = 0;
+    if (plan_conv_window(a, MODE, p.blob_bytes, cw, cw_smem))
+      return launch_conv_window(a, cw, cw_smem, reinterpret_cast<const __nv_bfloat16 *>(xt), blob, status, stream,
+                                reuse_flags, sms, device);
+  }
   const int cin_g = a.Cin / a.groups, K = a.Kh * a.Kw;
   const long long welems = (long long)a.groups * p.n_tiles * p.tile_n * cin_g * K;   // padding rows included
   if (!(reuse_flags & GACB_DCN_REUSE_WEIGHTS))
@@ -1264,12 +1694,6 @@ int launch_umma(const DcnArgs &a, const UmmaPlan &p, void *workspace, int32_t *s
   u.blob = blob;
   u.status = status;
   u.drop_weight_copies = (reuse_flags & kTestDropWeightCopies) ? 1 : 0;
-  int sms = 148, device = 0;
-  rc = check_cuda(cudaGetDevice(&device), "cudaGetDevice");
-  if (rc != GACB_OK) return rc;
-  rc = check_cuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device), "cudaDeviceGetAttribute(SM count)");
-  if (rc != GACB_OK) return rc;
-  if (device < 0 || device >= 64) return fail(GACB_ERR_UNSUPPORTED, "dcnv2: device ordinal %d is out of range", device);
   const UmmaLaunch shape = shape_umma_launch<MODE>(a, p, sms, u);
   const bool narrow = shape.narrow;
   const size_t smem = shape.smem;
@@ -1624,6 +2048,16 @@ GACB_API int gacb_dcnv2_launch_geometry(int n, int Cin, int H, int W, int Cout, 
   UmmaArgs u{};
   UmmaLaunch l;
   if (sm_count <= 0) sm_count = 148;
+  ConvWinArgs cw{};
+  size_t cw_smem = 0;
+  if (plan_conv_window(a, math_mode, p.blob_bytes, cw, cw_smem)) {
+    out->grid[0] = std::min(cw.tiles_total, sm_count); out->grid[1] = out->grid[2] = 1;
+    out->block[0] = kWinThreads; out->block[1] = out->block[2] = 1;
+    out->dynamic_smem_bytes = cw_smem;
+    out->units_per_cta = kTileM;      // per tile; a CTA takes tiles blockIdx.x, blockIdx.x + grid, ...
+    snprintf(out->kernel, sizeof(out->kernel), "conv_window_kernel");
+    return GACB_OK;
+  }
   switch (math_mode) {
     case MODE_BF16: l = shape_umma_launch<MODE_BF16>(a, p, sm_count, u); break;
     case MODE_TF32: l = shape_umma_launch<MODE_TF32>(a, p, sm_count, u); break;
@@ -1637,6 +2071,11 @@ GACB_API int gacb_dcnv2_launch_geometry(int n, int Cin, int H, int W, int Cout, 
            math_mode == MODE_BF16 ? "bf16" : (math_mode == MODE_TF32 ? "tf32" : "f32x3"), plain ? "plain" : "deform",
            l.narrow ? "narrow" : "wide");
   return GACB_OK;
+}
+
+GACB_API int gacb_conv_window_path(int mode) {
+  if (mode != 0 && mode != 1) return g_conv_window_path.load();
+  return g_conv_window_path.exchange(mode);
 }
 
 GACB_API int gacb_dcnv2_workspace_parts(int n, int Cin, int H, int W, int Cout, int Kh, int Kw, int sh, int sw, int pad_top,

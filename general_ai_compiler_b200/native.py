@@ -77,6 +77,7 @@ SIGNATURES = {
     "gacb_msda_offsets_logits_forward": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _ip] + [_i] * 7 + [_ip, _ip, _ip, _i, _i, _i, _i, _vp]),
     "gacb_msda_run": (_i, [ctypes.POINTER(MsdaDesc), _vp]),
     "gacb_msda_tile_path": (_i, [_i]),
+    "gacb_conv_window_path": (_i, [_i]),
     "gacb_dcnv2_forward": (_i, [_vp] * 6 + [_i] * 18 + [_vp, _sz, _vp, _vp]),
     "gacb_conv2d_forward": (_i, [_vp, _vp, _vp, _i, _vp, _vp] + [_i] * 20 + [_vp, _sz, _vp, _vp]),
     "gacb_conv2d_workspace_bytes": (_sz, [_i] * 17),

@@ -703,12 +703,13 @@ def conv2d_workspace_bytes(n_images, Cin, H, W, Cout, Kh, Kw, strides, pads, dil
 
 def conv2d_forward(x, weight, bias=None, *, strides=(1, 1), pads=(0, 0, 0, 0), dilations=(1, 1), groups=1,
                    math="f32x3", relu=False, split_at=None, out=None, n_range=None, workspace=None,
-                   status_word=None, stream=None, reuse_weights=False, reuse_input=False, input_at_end=False):
+                   status_word=None, stream=None, reuse_weights=False, reuse_input=False, input_at_end=False,
+                   test_flags=0):
     """Plain convolution on device tensors (float32, NCHW / OIHW) through the DCNv2 kernels with integer taps.
 
     ``split_at=c`` returns two tensors, channels ``[0, c)`` and ``[c, Cout)`` -- for BEVFormer's ``conv_offset``
     (``c = 2 * deform_groups * Kh * Kw``) these are DCNv2's ``offset`` and pre-sigmoid ``mask`` operands.
-    ``out`` is then a pair of tensors."""
+    ``out`` is then a pair of tensors.  ``test_flags`` is as in ``dcnv2_forward``."""
     torch = _torch()
     lib = native.load()
     if math not in native.DCN_MATH_MODES:
@@ -760,7 +761,7 @@ def conv2d_forward(x, weight, bias=None, *, strides=(1, 1), pads=(0, 0, 0, 0), d
                                      1 if relu else 0, y0.data_ptr(), y1.data_ptr() if y1 is not None else None, cut,
                                      N, Cin, H, W, Cout, Kh, Kw, strides[0], strides[1], pads[0], pads[1], pads[2],
                                      pads[3], dilations[0], dilations[1], groups, n0, n1,
-                                     native.DCN_MATH_MODES[math] | reuse, ws_ptr, ws_len,
+                                     native.DCN_MATH_MODES[math] | reuse | int(test_flags), ws_ptr, ws_len,
                                      status_word.data_ptr() if status_word is not None else None, _stream_ptr(stream))
         native.check(rc, "gacb_conv2d_forward")
     return out

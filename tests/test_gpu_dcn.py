@@ -2,6 +2,8 @@
 
 from __future__ import annotations
 
+import zlib
+
 import numpy as np
 import pytest
 
@@ -531,3 +533,84 @@ def test_conv2d_contract_violations(dev):
     rc = lib.gacb_conv2d_forward(x.data_ptr(), w.data_ptr(), None, 0, x.data_ptr(), None, 2, 1, 8, 6, 6, 4, 3, 3, 1, 1,
                                  1, 1, 1, 1, 1, 1, 1, 0, 1, 0, None, 0, None, None)
     assert rc == -1 and "split_at" in ops.native.last_error()
+
+
+# --------------------------------------------------------------------------- the window kernel of plain convolutions
+
+def _bf16_round(a):
+    import torch
+
+    return torch.from_numpy(np.ascontiguousarray(a)).to(torch.bfloat16).float().numpy()
+
+
+@pytest.fixture
+def window_path(dev):
+    """Calls ``use(mode)`` to switch the window kernel on or off; the library's mode is restored afterwards."""
+    _, ops, _ = dev
+    lib = ops.native.load()
+    before = lib.gacb_conv_window_path(-1)
+    yield lib.gacb_conv_window_path
+    lib.gacb_conv_window_path(before)
+
+
+@pytest.mark.parametrize("label,shape", [
+    # N, Cin, H, W, Cout, Kh, Kw, pads (top, left, bottom, right), relu
+    ("conv_offset_c4_cut", (2, 256, 58, 100, 27, 3, 3, (1, 1, 1, 1), False)),
+    ("ragged_tiles_cin192", (3, 192, 37, 45, 27, 3, 3, (1, 1, 1, 1), True)),        # three 64-channel groups, partial tiles
+    ("kernel_5x5_cin64", (1, 64, 40, 44, 64, 5, 5, (2, 2, 2, 2), False)),           # two 32-column accumulator slabs
+    ("uneven_pads_cin128", (2, 128, 33, 50, 16, 3, 3, (0, 2, 1, 0), False)),
+    ("one_by_one_cin256", (1, 256, 64, 64, 32, 1, 1, (0, 0, 0, 0), True)),
+    ("no_padding_cin384", (1, 384, 30, 41, 27, 3, 3, (0, 0, 0, 0), False)),         # three 128-channel groups
+])
+def test_window_kernel_matches_the_oracle_on_bf16_operands(dev, window_path, label, shape):
+    """BF16 mode rounds X and W to bf16 and accumulates in float32, so the oracle on the rounded operands must agree
+    at the float32 gate; the gather kernel must agree with the window kernel to the same gate."""
+    from oracle import conv2d_c
+
+    torch, ops, device = dev
+    n, cin, h, w_, cout, kh, kw, pads, relu = shape
+    rng = np.random.default_rng(zlib.crc32(label.encode()))
+    x = rng.standard_normal((n, cin, h, w_)).astype(np.float32)
+    w = (rng.standard_normal((cout, cin, kh, kw)) * np.sqrt(2.0 / (kh * kw * cin))).astype(np.float32)
+    b = rng.standard_normal(cout).astype(np.float32)
+    c = {"X": x, "W": w, "bias": b, "attrs": np.asarray([1, 1, *pads, 1, 1, 1, int(relu)], np.int32)}
+    geo = ops.native.dcnv2_launch_geometry(n, cin, h, w_, cout, kh, kw, (1, 1), pads[:2], (1, 1), 1, 1, ops.native.DCN_BF16,
+                                           plain=True)
+    window_path(1)
+    got = _run_conv(dev, c, "bf16").cpu().numpy()
+    want = conv2d_c(_bf16_round(x), _bf16_round(w), b, pads=pads, relu=relu)
+    assert_fp32_gate(got, want, f"{label} window kernel")
+    window_path(0)
+    gathered = _run_conv(dev, c, "bf16").cpu().numpy()
+    assert_fp32_gate(gathered, want, f"{label} gather kernel")
+    if pads[0] == pads[2] and pads[1] == pads[3]:      # the geometry query takes symmetric pads
+        assert geo.kernel == b"conv_window_kernel" and geo.block[0] == 544 and geo.grid[0] <= 148
+
+
+def test_window_kernel_split_outputs_sharding_and_weight_reuse(dev, window_path):
+    """offset/mask split outputs, image-range calls bit-identical to one call, packed weights reused across calls."""
+    torch, ops, device = dev
+    window_path(1)
+    rng = np.random.default_rng(9)
+    x = torch.from_numpy(rng.standard_normal((4, 64, 29, 36)).astype(np.float32)).to(device)
+    w = torch.from_numpy((rng.standard_normal((27, 64, 3, 3)) * 0.05).astype(np.float32)).to(device)
+    b = torch.from_numpy(rng.standard_normal(27).astype(np.float32)).to(device)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    whole = ops.conv2d_forward(x, w, b, pads=(1, 1, 1, 1), math="bf16", status_word=status)
+    off, mask = ops.conv2d_forward(x, w, b, pads=(1, 1, 1, 1), math="bf16", split_at=18, status_word=status)
+    assert torch.equal(off, whole[:, :18]) and torch.equal(mask, whole[:, 18:])
+    out = torch.full_like(whole, float("nan"))
+    for n0, n1 in ((0, 1), (1, 4)):
+        ops.conv2d_forward(x, w, b, pads=(1, 1, 1, 1), math="bf16", n_range=(n0, n1), out=out, status_word=status)
+    assert torch.equal(out, whole)
+    need = ops.conv2d_workspace_bytes(4, 64, 29, 36, 27, 3, 3, (1, 1), (1, 1, 1, 1), (1, 1), 1, "bf16")
+    ws = torch.empty(need, dtype=torch.uint8, device=device)
+    first = ops.conv2d_forward(x, w, b, pads=(1, 1, 1, 1), math="bf16", workspace=ws, status_word=status)
+    again = ops.conv2d_forward(x, w, b, pads=(1, 1, 1, 1), math="bf16", workspace=ws, reuse_weights=True, reuse_input=True,
+                               status_word=status)
+    torch.cuda.synchronize()
+    assert torch.equal(first, whole) and torch.equal(again, whole) and int(status.item()) == 0
+    # a strided convolution does not qualify and still runs (another kernel)
+    strided = ops.conv2d_forward(x, w, b, strides=(2, 2), pads=(1, 1, 1, 1), math="bf16", status_word=status)
+    ref = torch.nn.functional.conv2d(x.double(), w.double(), b.double(), stride=2, padding=1)
+    assert_rel_gate(strided.cpu().numpy(), ref.float().cpu().numpy(), 1e-2, "strided falls back")

@@ -90,6 +90,34 @@ def test_expired_wait_sets_the_status_word_and_the_gpu_stays_usable(math, dev, f
         assert float(np.abs(good.cpu().numpy() - want).max()) <= 1e-2 * float(np.abs(want).max())
 
 
+def test_expired_wait_in_the_window_kernel_of_plain_convolutions(dev, fault_build):
+    """The persistent window kernel has its own pipeline (window ring, weight ring, two accumulator sets): with the
+    weight copies dropped its tensor-core thread gives up on the first stage, every role unwinds, the status word is
+    set, and the next call of the same kernel is correct."""
+    torch, ops, device = dev
+    from general_ai_compiler_b200 import native
+    from oracle import conv2d_c
+
+    rng = np.random.default_rng(31)
+    x = rng.standard_normal((2, 64, 40, 30)).astype(np.float32)
+    w = (rng.standard_normal((27, 64, 3, 3)) * 0.05).astype(np.float32)
+    geo = native.dcnv2_launch_geometry(2, 64, 40, 30, 27, 3, 3, (1, 1), (1, 1), (1, 1), 1, 1, native.DCN_BF16, plain=True)
+    assert geo.kernel == b"conv_window_kernel"
+    xd, wd = torch.from_numpy(x).to(device), torch.from_numpy(w).to(device)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    ops.conv2d_forward(xd, wd, None, pads=(1, 1, 1, 1), math="bf16", status_word=status,
+                       test_flags=native.DCN_TEST_DROP_WEIGHT_COPIES)
+    torch.cuda.synchronize()                      # the kernel came back by itself
+    assert int(status.item()) == 1
+    assert fault_build.gacb_read_status_word(status.data_ptr(), None) == native.GACB_ERR_DEVICE_TIMEOUT
+    status.zero_()
+    good = ops.conv2d_forward(xd, wd, None, pads=(1, 1, 1, 1), math="bf16", status_word=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    rounded = [torch.from_numpy(v).to(torch.bfloat16).float().numpy() for v in (x, w)]
+    assert_fp32_gate(good.cpu().numpy(), conv2d_c(rounded[0], rounded[1], None, pads=(1, 1, 1, 1)), "after an expired wait")
+
+
 def test_session_raises_and_invalidates_itself_after_an_expired_wait(dev, fault_build):
     torch, ops, device = dev
     from general_ai_compiler_b200 import native
