@@ -1207,8 +1207,36 @@ __global__ void __launch_bounds__(CtaShape<NARROW>::kThreads, CtaShape<NARROW>::
 // accumulator (a partial sum); the epilogue adds the partial sums.  Two such sets sit in tensor memory, so that a
 // tile's stores overlap the next tile's products.
 //
-// BF16 mode only (operands rounded to bf16, float32 accumulation), whole images, groups = 1, stride = dilation = 1,
-// at most 64 output channels, bias and ReLU only.
+// Whole images, groups = 1, stride = dilation = 1, at most 64 output channels (32 in F32X3 mode), bias and ReLU
+// only.  The three math modes differ in what a window holds:
+//   BF16   the bf16 channel-last copy as it is (8 channels per 16-byte chunk, K = 16 per MMA);
+//   TF32   the float32 channel-last copy as it is (4 channels per chunk, K = 8 per MMA); the tensor core reads the
+//          upper 19 bits of each float, i.e. the activations are truncated to tf32 here where the gather kernel
+//          rounds them to nearest (the weights are rounded to nearest in both);
+//   F32X3  two windows made by the fill from the float32 copy, hi = bf16(x) and lo = bf16(x - hi), and three
+//          products per slice, hi*Whi into a main accumulator, lo*Whi + hi*Wlo into a cross accumulator: the gather
+//          kernel's arithmetic.
+template <int MODE>
+struct WinTraits;
+template <>
+struct WinTraits<MODE_BF16> {
+  using Xt = __nv_bfloat16;
+  static constexpr int kChunkCh = 8, kParts = 1;
+  static constexpr bool kTf32 = false;
+};
+template <>
+struct WinTraits<MODE_TF32> {
+  using Xt = float;
+  static constexpr int kChunkCh = 4, kParts = 1;
+  static constexpr bool kTf32 = true;
+};
+template <>
+struct WinTraits<MODE_F32X3> {
+  using Xt = float;
+  static constexpr int kChunkCh = 8, kParts = 2;
+  static constexpr bool kTf32 = false;
+};
+__host__ __device__ inline int win_chunk_channels(int mode) { return mode == MODE_TF32 ? 4 : 8; }
 constexpr int kWinTileH = 16, kWinTileW = 8;          // pixels of a tile: 16 rows x 8 columns = 128 MMA rows
 constexpr int kWinFillWarps = 8, kWinEpiWarps = 4;
 constexpr int kWinAccs = 4;                           // accumulators per tile = issuing threads (one warp each)
@@ -1220,18 +1248,21 @@ static_assert(kWinTileH * kWinTileW == kTileM, "a tile is one 128-row MMA");
 
 struct ConvWinArgs {
   DcnArgs d;
-  const __nv_bfloat16 *xt;      // channel-last bf16 copy of images [n_begin, n_end)
-  const unsigned char *blob;    // packed weights: [channel group][kernel point][8-channel chunk][n_pad rows][8]
+  const void *xt;               // channel-last copy of images [n_begin, n_end): bf16 in BF16 mode, else float32
+  const unsigned char *blob;    // packed weights: [channel group][kernel point][part][chunk][n_pad rows][16 bytes]
   int32_t *status;
   int n_pad;                    // MMA N: output channels rounded up to 32
   int tiles_x, tiles_y, tiles_total;
-  int cgroups, cg_channels;     // channel groups per tile and channels per group (64 or 128)
+  int cgroups, cg_channels;     // channel groups per tile and channels per group (8 or 16 chunks)
+  int chunks;                   // 16-byte chunks per texel of a window
   int win_h, win_w, win_texels;
   int chunk_stride;             // bytes between the 8-channel chunks of a window: an odd number of 16-byte units, so
                                 // that the fill's 16 lanes of one texel (one per chunk) spread over all banks
   int stage_kps, cg_stages;     // kernel points per weight stage; stages per channel group
   int win_bufs, b_stages;       // ring depths
-  unsigned win_bytes, kp_bytes, b_stage_bytes;
+  unsigned win_part_bytes, win_bytes;      // one part of a window (hi or lo); all parts
+  unsigned kp_part_bytes, kp_bytes;        // weights of one kernel point: one part; all parts
+  unsigned b_stage_bytes;
   int tmem_cols;
   int drop_weight_copies;       // test build only (GACB_DCN_FAULT_INJECT): the loader skips every copy
 };
@@ -1247,8 +1278,10 @@ __device__ __forceinline__ uint64_t umma_smem_desc_plain(uint32_t smem_addr, uin
   return d;
 }
 
+template <int MODE>
 __global__ void __launch_bounds__(256) conv_window_pack_weights(const float *__restrict__ w, unsigned char *__restrict__ blob,
                                                                int Cout, int Cin, int K, int n_pad, int cg_channels) {
+  using T = WinTraits<MODE>;
   const long long total = (long long)n_pad * Cin * K;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
@@ -1257,12 +1290,21 @@ __global__ void __launch_bounds__(256) conv_window_pack_weights(const float *__r
   const int n = (int)(i / ((long long)Cin * K));
   const float v = n < Cout ? __ldg(w + ((long long)n * Cin + ci) * K + kp) : 0.0f;
   const int cg = ci / cg_channels, cc = ci - cg * cg_channels;
-  const size_t per_kp = (size_t)(cg_channels / 8) * n_pad * 16;
-  const size_t byte = ((size_t)cg * K + kp) * per_kp + ((size_t)(cc >> 3) * n_pad + n) * 16 + (cc & 7) * 2;
-  *reinterpret_cast<__nv_bfloat16 *>(blob + byte) = __float2bfloat16_rn(v);
+  const size_t part = (size_t)(cg_channels / T::kChunkCh) * n_pad * 16;
+  unsigned char *at = blob + ((size_t)cg * K + kp) * (T::kParts * part) + ((size_t)(cc / T::kChunkCh) * n_pad + n) * 16;
+  if (T::kTf32) {
+    reinterpret_cast<float *>(at)[cc % T::kChunkCh] = tf32_round(v);
+  } else {
+    const __nv_bfloat16 hi = __float2bfloat16_rn(v);
+    reinterpret_cast<__nv_bfloat16 *>(at)[cc % T::kChunkCh] = hi;
+    if (T::kParts == 2) reinterpret_cast<__nv_bfloat16 *>(at + part)[cc % T::kChunkCh] = __float2bfloat16_rn(v - __bfloat162float(hi));
+  }
 }
 
+template <int MODE>
 __global__ void __launch_bounds__(kWinThreads, 1) conv_window_kernel(const __grid_constant__ ConvWinArgs u) {
+  using T = WinTraits<MODE>;
+  using Xt = typename T::Xt;
   extern __shared__ unsigned char smem_raw[];
   unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~(uintptr_t)127);
   const DcnArgs &a = u.d;
@@ -1310,34 +1352,65 @@ __global__ void __launch_bounds__(kWinThreads, 1) conv_window_kernel(const __gri
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int set_cols = kWinAccs * u.n_pad;      // tensor-memory columns of one tile's accumulators
+  const int set_cols = T::kParts * kWinAccs * u.n_pad;      // tensor-memory columns of one tile's accumulators
 
   if (warp >= kWinFirstFillWarp) {
     // ------------------------------------------------------------------ window fill (eight warps)
     // A thread copies the 16-byte pieces (texel, chunk) with chunk = ft % chunks (neighbouring lanes read one texel's
     // channels) and texel = ft / chunks, + 256 / chunks, ...; chunks is 8 or 16, so nothing below divides.
     const int ft = tid - kWinFirstFillWarp * 32;                    // 0 .. 255
-    const int chunks = u.cg_channels / 8, chunk_shift = chunks == 16 ? 4 : 3;
+    const int chunks = u.chunks, chunk_shift = chunks == 16 ? 4 : 3;
     const int c = ft & (chunks - 1), tt0 = ft >> chunk_shift, tt_step = (kWinFillWarps * 32) >> chunk_shift;
     const int wy0 = tt0 / u.win_w, wx0 = tt0 - wy0 * u.win_w;
     bool alive = true;
     int buf = 0, round = 0;                                         // ring position: step % win_bufs, step / win_bufs
+    // The copies of a window are one cp.async group; a window is handed over (fence, arrive) only after the NEXT
+    // window's copies have been issued, so that two windows' worth of copies overlap their latency.
+    int pending = -1;                                               // buffer whose copies are in flight
+    auto hand_over = [&](int which) {
+      fence_proxy_async_smem();      // generic-proxy writes -> visible to the tensor core's async proxy
+      __syncwarp();                  // one arrival per warp, after every lane's writes are fenced
+      if (lane == 0) mbar_arrive(win_full(which));
+    };
     for (int t = blockIdx.x; t < u.tiles_total; t += gridDim.x) {
       const int img = t / tiles_per_image, r = t - img * tiles_per_image;
       const int ty = r / u.tiles_x, tx = r - ty * u.tiles_x;
       const int y0 = ty * kWinTileH - a.ph, x0 = tx * kWinTileW - a.pw;     // input position of window texel (0, 0)
-      const __nv_bfloat16 *image = u.xt + (size_t)img * a.H * a.W * a.Cin;
+      const Xt *image = static_cast<const Xt *>(u.xt) + (size_t)img * a.H * a.W * a.Cin;
       for (int cg = 0; cg < u.cgroups; ++cg) {
         if (alive) alive = mbar_wait_warp(win_empty(buf), (round & 1) ^ 1, abort_flag, lane);
         if (alive) {
           unsigned char *win = windows + (size_t)buf * u.win_bytes;
           unsigned char *dst = win + (size_t)c * u.chunk_stride + (size_t)tt0 * 16;
-          const __nv_bfloat16 *src = image + cg * u.cg_channels + c * 8;
+          const Xt *src = image + cg * u.cg_channels + c * T::kChunkCh;
           int wy = wy0, wx = wx0;
+#pragma unroll 4
           for (int tt = tt0; tt < u.win_texels; tt += tt_step, dst += tt_step * 16) {
             const int gy = y0 + wy, gx = x0 + wx;
-            if (gy >= 0 && gy < a.H && gx >= 0 && gx < a.W) {
-              const int e = (int)GACB_INDEX((gy * a.W + gx) * a.Cin, (long long)a.H * a.W * a.Cin, 12);
+            const bool inside = gy >= 0 && gy < a.H && gx >= 0 && gx < a.W;
+            const int e = inside ? (int)GACB_INDEX((gy * a.W + gx) * a.Cin, (long long)a.H * a.W * a.Cin, 12) : 0;
+            if constexpr (T::kParts == 2) {
+              // eight float32 channels -> bf16 hi and lo pieces of the two windows
+              uint4 hi = make_uint4(0u, 0u, 0u, 0u), lo = hi;
+              if (inside) {
+                const float4 v0 = __ldg(reinterpret_cast<const float4 *>(src + e));
+                const float4 v1 = __ldg(reinterpret_cast<const float4 *>(src + e) + 1);
+                const float x[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                uint32_t h[4], l[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                  const __nv_bfloat16 h0 = __float2bfloat16_rn(x[2 * k]), h1 = __float2bfloat16_rn(x[2 * k + 1]);
+                  const __nv_bfloat16 l0 = __float2bfloat16_rn(x[2 * k] - __bfloat162float(h0));
+                  const __nv_bfloat16 l1 = __float2bfloat16_rn(x[2 * k + 1] - __bfloat162float(h1));
+                  h[k] = (uint32_t)__bfloat16_as_ushort(h0) | ((uint32_t)__bfloat16_as_ushort(h1) << 16);
+                  l[k] = (uint32_t)__bfloat16_as_ushort(l0) | ((uint32_t)__bfloat16_as_ushort(l1) << 16);
+                }
+                hi = make_uint4(h[0], h[1], h[2], h[3]);
+                lo = make_uint4(l[0], l[1], l[2], l[3]);
+              }
+              *reinterpret_cast<uint4 *>(dst) = hi;
+              *reinterpret_cast<uint4 *>(dst + u.win_part_bytes) = lo;
+            } else if (inside) {
               async_copy_16(smem_u32(dst), src + e);
             } else {
               *reinterpret_cast<uint4 *>(dst) = make_uint4(0u, 0u, 0u, 0u);   // zero padding
@@ -1345,16 +1418,22 @@ __global__ void __launch_bounds__(kWinThreads, 1) conv_window_kernel(const __gri
             wx += tt_step;
             while (wx >= u.win_w) { wx -= u.win_w; ++wy; }
           }
-          async_copy_commit();
-          async_copy_wait_all();
-          fence_proxy_async_smem();      // generic-proxy writes -> visible to the tensor core's async proxy
+          if constexpr (T::kParts == 1) {
+            async_copy_commit();
+            if (pending >= 0) {
+              async_copy_wait_all_but_one();
+              hand_over(pending);
+            }
+            pending = buf;
+          } else {
+            hand_over(buf);            // written with plain stores: complete
+          }
         }
-        // one arrival per warp, after every lane's writes are fenced
-        const bool warp_alive = __all_sync(0xffffffffu, alive);
-        if (warp_alive && lane == 0) mbar_arrive(win_full(buf));
         if (++buf == u.win_bufs) { buf = 0; ++round; }
       }
     }
+    async_copy_wait_all();             // nothing of this thread may be in flight when the CTA ends
+    if (alive && pending >= 0) hand_over(pending);
   } else if (warp == kWinLoaderWarp) {
     // ------------------------------------------------------------------ weight loader (one lane)
     if (lane == 0) {
@@ -1388,19 +1467,22 @@ __global__ void __launch_bounds__(kWinThreads, 1) conv_window_kernel(const __gri
     // ------------------------------------------------------------------ MMA issuers (one lane of each of kWinAccs warps)
     if (lane == 0) {
       const int issuer = warp - kWinMmaWarp;          // takes the 16-channel slices issuer, issuer + kWinAccs, ...
-      const uint32_t idesc = umma_idesc(1, kTileM, u.n_pad);
+      const uint32_t idesc = umma_idesc(T::kTf32 ? 2 : 1, kTileM, u.n_pad);
       const uint32_t a_lbo = (uint32_t)u.chunk_stride, a_sbo = (uint32_t)u.win_w * 16u;
       const uint32_t b_lbo = (uint32_t)u.n_pad * 16u, b_sbo = 128u;
       // descriptors with a zero start address; a start address is added in 16-byte units
       const uint64_t a_desc0 = umma_smem_desc_plain(0, a_lbo, a_sbo), b_desc0 = umma_smem_desc_plain(0, b_lbo, b_sbo);
-      const uint32_t a_k16 = (2u * a_lbo) >> 4, b_k16 = (2u * b_lbo) >> 4;     // one 16-channel slice, in 16-byte units
-      const int k16_quads = u.cg_channels / (16 * kWinAccs);
+      // one slice = the two chunks an MMA reads along K (16 channels, 8 in TF32 mode), in 16-byte units
+      const uint32_t a_k16 = (2u * a_lbo) >> 4, b_k16 = (2u * b_lbo) >> 4;
+      const int k16_quads = u.chunks / (2 * kWinAccs);
+      const uint32_t a_lo = u.win_part_bytes >> 4, b_lo = u.kp_part_bytes >> 4;     // F32X3: from the hi part to the lo part
       bool ok = true;
       int buf = 0, wround = 0, s = 0, bround = 0, it = 0;
       for (int t = blockIdx.x; t < u.tiles_total && ok; t += gridDim.x, ++it) {
         const int set = it & 1, use = it >> 1;
         ok = mbar_wait(acc_empty(set), (use & 1) ^ 1, abort_flag);    // the epilogue has read this set's last tile
         const uint32_t acc = tmem_base + (uint32_t)(set * set_cols + issuer * u.n_pad);
+        const uint32_t acc_cross = acc + (uint32_t)(kWinAccs * u.n_pad);   // F32X3 only
         uint32_t accumulate = 0;                                      // 0 for the first MMA into the accumulator
         for (int cg = 0; cg < u.cgroups && ok; ++cg) {
           ok = mbar_wait(win_full(buf), wround & 1, abort_flag);
@@ -1411,11 +1493,16 @@ __global__ void __launch_bounds__(kWinThreads, 1) conv_window_kernel(const __gri
             if (!ok) break;
             tc_fence_after();
             const int k1 = min(K, k0 + u.stage_kps);
-            uint64_t bd = b_desc0 + (uint64_t)(smem_u32(b_ring + (size_t)s * u.b_stage_bytes) >> 4) + issuer * b_k16;
+            const uint64_t bd0 = b_desc0 + (uint64_t)(smem_u32(b_ring + (size_t)s * u.b_stage_bytes) >> 4) + issuer * b_k16;
             for (int kp = k0; kp < k1; ++kp) {
               uint64_t ad = a_desc0 + (uint64_t)((win + (uint32_t)(ky * u.win_w + kx) * 16u) >> 4) + issuer * a_k16;
+              uint64_t bd = bd0 + (uint64_t)(kp - k0) * (u.kp_bytes >> 4);
               for (int q = 0; q < k16_quads; ++q) {
-                umma_ss<false>(acc, ad, bd, idesc, accumulate);
+                umma_ss<T::kTf32>(acc, ad, bd, idesc, accumulate);
+                if constexpr (T::kParts == 2) {
+                  umma_ss<false>(acc_cross, ad + a_lo, bd, idesc, accumulate);
+                  umma_ss<false>(acc_cross, ad, bd + b_lo, idesc, 1u);
+                }
                 accumulate = 1u;
                 ad += kWinAccs * a_k16;
                 bd += kWinAccs * b_k16;
@@ -1461,13 +1548,13 @@ __global__ void __launch_bounds__(kWinThreads, 1) conv_window_kernel(const __gri
                               : nullptr;
       const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(set * set_cols);
       for (int col = 0; col < u.n_pad; col += 32) {
-        // the tile's value is the sum of its kWinAccs partial accumulators
+        // the tile's value is the sum of its partial accumulators (main ones first, then F32X3's cross ones)
         uint32_t rr[32], xa[32];
         tmem_ld32(lane_base + (uint32_t)col, rr);
         tmem_ld32(lane_base + (uint32_t)(u.n_pad + col), xa);
         tmem_ld_wait();
 #pragma unroll
-        for (int p = 2; p < kWinAccs; ++p) {
+        for (int p = 2; p < T::kParts * kWinAccs; ++p) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) rr[j] = __float_as_uint(__fadd_rn(__uint_as_float(rr[j]), __uint_as_float(xa[j])));
           tmem_ld32(lane_base + (uint32_t)(p * u.n_pad + col), xa);
@@ -1514,25 +1601,30 @@ __global__ void __launch_bounds__(kWinThreads, 1) conv_window_kernel(const __gri
 // 0 = plain convolutions always take the gather kernel; 1 (default) = the window kernel where it applies.
 std::atomic<int> g_conv_window_path{1};
 
-// Does the window kernel apply, and with which shape?  (BF16 mode, plain convolution over whole images.)
+// Does the window kernel apply, and with which shape?  (Plain convolution over whole images.)
 bool plan_conv_window(const DcnArgs &a, int mode, size_t blob_capacity, ConvWinArgs &u, size_t &smem) {
   if (!g_conv_window_path.load(std::memory_order_relaxed)) return false;
   const bool whole = a.m_first == 0 && a.row_begin == 0 && a.row_end == a.Ho &&
                      a.m_count == (long long)(a.n_end - a.n_begin) * a.Ho * a.Wo;
-  if (mode != MODE_BF16 || a.offset != nullptr || !whole || a.bn_scale != nullptr) return false;
+  if (a.offset != nullptr || !whole || a.bn_scale != nullptr) return false;
   if (a.groups != 1 || a.sh != 1 || a.sw != 1 || a.dh != 1 || a.dw != 1) return false;
-  if (a.Cout > 64 || a.Cin % 64 || a.Kh * a.Kw > 49) return false;
+  const int chunk_ch = win_chunk_channels(mode), parts = parts_of(mode);
+  // a channel group is 8 or 16 chunks of a texel; F32X3 keeps two windows per group and takes the smaller one
+  if (a.Cout > (parts == 2 ? 32 : 64) || a.Cin % (8 * chunk_ch) || a.Kh * a.Kw > 49) return false;
   if ((long long)(a.n_end - a.n_begin) * a.H * a.W * a.Cin > 2147483647LL) return false;
   const int K = a.Kh * a.Kw;
   u.n_pad = (a.Cout + 31) / 32 * 32;
-  u.cg_channels = a.Cin % 128 == 0 ? 128 : 64;
+  u.chunks = (parts == 1 && a.Cin % (16 * chunk_ch) == 0) ? 16 : 8;
+  u.cg_channels = u.chunks * chunk_ch;
   u.cgroups = a.Cin / u.cg_channels;
   u.win_h = kWinTileH + a.Kh - 1;
   u.win_w = kWinTileW + a.Kw - 1;
   u.win_texels = u.win_h * u.win_w;
   u.chunk_stride = (u.win_texels | 1) * 16;
-  u.win_bytes = (unsigned)(((size_t)(u.cg_channels / 8) * u.chunk_stride + 127) / 128 * 128);
-  u.kp_bytes = (unsigned)((size_t)(u.cg_channels / 8) * u.n_pad * 16);
+  u.win_part_bytes = (unsigned)(((size_t)u.chunks * u.chunk_stride + 127) / 128 * 128);
+  u.win_bytes = (unsigned)parts * u.win_part_bytes;
+  u.kp_part_bytes = (unsigned)((size_t)u.chunks * u.n_pad * 16);
+  u.kp_bytes = (unsigned)parts * u.kp_part_bytes;
   u.stage_kps = std::max(1, std::min(K, kWinStageBytes / (int)u.kp_bytes));
   u.cg_stages = (K + u.stage_kps - 1) / u.stage_kps;
   u.b_stage_bytes = (unsigned)u.stage_kps * u.kp_bytes;
@@ -1551,17 +1643,19 @@ bool plan_conv_window(const DcnArgs &a, int mode, size_t blob_capacity, ConvWinA
   u.tiles_y = (a.Ho + kWinTileH - 1) / kWinTileH;
   u.tiles_total = (a.n_end - a.n_begin) * u.tiles_x * u.tiles_y;
   int cols = 32;
-  while (cols < 2 * kWinAccs * u.n_pad) cols <<= 1;
-  u.tmem_cols = cols;      // at most 2 * 4 * 64 = 512 columns
+  while (cols < 2 * parts * kWinAccs * u.n_pad) cols <<= 1;
+  u.tmem_cols = cols;      // at most 2 * 4 * 64 = 2 * 2 * 4 * 32 = 512 columns
   return true;
 }
 
-int launch_conv_window(const DcnArgs &a, ConvWinArgs &u, size_t smem, const __nv_bfloat16 *xt, unsigned char *blob,
+template <int MODE>
+int launch_conv_window(const DcnArgs &a, ConvWinArgs &u, size_t smem, const void *xt, unsigned char *blob,
                        int32_t *status, cudaStream_t stream, int reuse_flags, int sms, int device) {
   const int K = a.Kh * a.Kw;
   if (!(reuse_flags & GACB_DCN_REUSE_WEIGHTS)) {
     const long long welems = (long long)u.n_pad * a.Cin * K;
-    conv_window_pack_weights<<<(int)((welems + 255) / 256), 256, 0, stream>>>(a.w, blob, a.Cout, a.Cin, K, u.n_pad, u.cg_channels);
+    conv_window_pack_weights<MODE><<<(int)((welems + 255) / 256), 256, 0, stream>>>(a.w, blob, a.Cout, a.Cin, K, u.n_pad,
+                                                                                  u.cg_channels);
     const int rc = check_cuda(cudaGetLastError(), "conv_window_pack_weights launch");
     if (rc != GACB_OK) return rc;
   }
@@ -1570,19 +1664,20 @@ int launch_conv_window(const DcnArgs &a, ConvWinArgs &u, size_t smem, const __nv
   u.blob = blob;
   u.status = status;
   u.drop_weight_copies = (reuse_flags & kTestDropWeightCopies) ? 1 : 0;
-  static std::mutex attr_lock;
+  static std::mutex attr_lock;      // one flag set per math mode (this function is a template)
   static bool attr_done[64] = {};
   {
     std::lock_guard<std::mutex> guard(attr_lock);
     if (!attr_done[device]) {
-      const int rc = check_cuda(cudaFuncSetAttribute(conv_window_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024),
+      const int rc = check_cuda(cudaFuncSetAttribute(conv_window_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                     227 * 1024),
                                 "cudaFuncSetAttribute(conv_window_kernel)");
       if (rc != GACB_OK) return rc;
       attr_done[device] = true;
     }
   }
   const int grid = std::min(u.tiles_total, sms);
-  conv_window_kernel<<<grid, kWinThreads, smem, stream>>>(u);
+  conv_window_kernel<MODE><<<grid, kWinThreads, smem, stream>>>(u);
   return check_cuda(cudaGetLastError(), "conv_window_kernel launch");
 }
 
@@ -1672,13 +1767,12 @@ int launch_umma(const DcnArgs &a, const UmmaPlan &p, void *workspace, int32_t *s
   rc = check_cuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device), "cudaDeviceGetAttribute(SM count)");
   if (rc != GACB_OK) return rc;
   if (device < 0 || device >= 64) return fail(GACB_ERR_UNSUPPORTED, "dcnv2: device ordinal %d is out of range", device);
-  if constexpr (MODE == MODE_BF16) {
+  {
     // a plain convolution with few output channels reads shifted windows instead of gathering (its own weight layout)
     ConvWinArgs cw{};
     size_t cw_smem = 0;
     if (plan_conv_window(a, MODE, p.blob_bytes, cw, cw_smem))
-      return launch_conv_window(a, cw, cw_smem, reinterpret_cast<const __nv_bfloat16 *>(xt), blob, status, stream,
-                                reuse_flags, sms, device);
+      return launch_conv_window<MODE>(a, cw, cw_smem, xt, blob, status, stream, reuse_flags, sms, device);
   }
   const int cin_g = a.Cin / a.groups, K = a.Kh * a.Kw;
   const long long welems = (long long)a.groups * p.n_tiles * p.tile_n * cin_g * K;   // padding rows included
@@ -2055,7 +2149,8 @@ GACB_API int gacb_dcnv2_launch_geometry(int n, int Cin, int H, int W, int Cout, 
     out->block[0] = kWinThreads; out->block[1] = out->block[2] = 1;
     out->dynamic_smem_bytes = cw_smem;
     out->units_per_cta = kTileM;      // per tile; a CTA takes tiles blockIdx.x, blockIdx.x + grid, ...
-    snprintf(out->kernel, sizeof(out->kernel), "conv_window_kernel");
+    snprintf(out->kernel, sizeof(out->kernel), "conv_window_kernel<%s>",
+             math_mode == MODE_BF16 ? "bf16" : (math_mode == MODE_TF32 ? "tf32" : "f32x3"));
     return GACB_OK;
   }
   switch (math_mode) {

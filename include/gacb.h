@@ -239,14 +239,16 @@ size_t gacb_conv2d_workspace_bytes(int n, int Cin, int H, int W, int Cout, int K
                                    int pad_top, int pad_left, int pad_bottom, int pad_right, int dh, int dw,
                                    int groups, int math_mode);
 
-/* Kernel choice for plain convolutions with few output channels in BF16 mode.  A whole-image call with
- * groups = 1, stride = dilation = 1, Cout <= 64, Cin a multiple of 64 and no BatchNorm runs a persistent kernel
- * that stages each 16 x 8 pixel tile's input window in shared memory once and feeds the tensor core shifted views
- * of it, one per kernel point, instead of gathering every tap (BEVFormer's 27-channel conv_offset:
- * src/gac/models/bevformer/resnet_dcn.py:131-134).  Same operands and rounding as the gather kernel (bf16
- * operands, float32 accumulation); only the order of the float32 additions differs.  The packed weights in the
- * workspace have this kernel's own layout, so GACB_DCN_REUSE_WEIGHTS calls must run under the mode the weights
- * were packed under.  No reference counterpart (a tuning knob):
+/* Kernel choice for plain convolutions with few output channels.  A whole-image call with groups = 1,
+ * stride = dilation = 1, Cout <= 64 (32 in F32X3 mode), Cin a multiple of 64 (32 in TF32 mode) and no BatchNorm
+ * runs a persistent kernel that stages each 16 x 8 pixel tile's input window in shared memory once and feeds the
+ * tensor core shifted views of it, one per kernel point, instead of gathering every tap (BEVFormer's 27-channel
+ * conv_offset: src/gac/models/bevformer/resnet_dcn.py:131-134).  Operands and products are those of the gather
+ * kernel in the same math mode, with two differences: the order of the float32 additions, and in TF32 mode the
+ * activations are truncated to tf32 (the tensor core reads the upper 19 bits of the float32 copy) where the gather
+ * kernel rounds them to nearest.  The packed weights in the workspace have this kernel's own layout, so
+ * GACB_DCN_REUSE_WEIGHTS calls must run under the mode the weights were packed under.  No reference counterpart
+ * (a tuning knob):
  *   gacb_conv_window_path(mode)    mode 0 = always the gather kernel, 1 = the window kernel where it applies
  *                                  (default), any other value = leave unchanged; returns the previous mode.
  *                                  Process-wide. */

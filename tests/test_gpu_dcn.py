@@ -584,7 +584,52 @@ def test_window_kernel_matches_the_oracle_on_bf16_operands(dev, window_path, lab
     gathered = _run_conv(dev, c, "bf16").cpu().numpy()
     assert_fp32_gate(gathered, want, f"{label} gather kernel")
     if pads[0] == pads[2] and pads[1] == pads[3]:      # the geometry query takes symmetric pads
-        assert geo.kernel == b"conv_window_kernel" and geo.block[0] == 544 and geo.grid[0] <= 148
+        assert geo.kernel == b"conv_window_kernel<bf16>" and geo.block[0] == 544 and geo.grid[0] <= 148
+
+
+def _tf32_truncate(a):
+    bits = np.ascontiguousarray(a, np.float32).view(np.uint32) & np.uint32(0xFFFFE000)
+    return bits.view(np.float32)
+
+
+def _tf32_round_nearest(a):
+    """cvt.rna: nearest tf32, ties away from zero (the bit pattern is sign-magnitude, so adding half an ulp rounds the
+    magnitude)."""
+    bits = np.ascontiguousarray(a, np.float32).view(np.uint32)
+    return ((bits + np.uint32(0x1000)) & np.uint32(0xFFFFE000)).view(np.float32)
+
+
+@pytest.mark.parametrize("label,shape", [
+    ("conv_offset_c4_cut", (2, 256, 58, 100, 27, 3, 3, (1, 1, 1, 1), False)),
+    ("ragged_tiles_cin96", (3, 96, 37, 45, 27, 3, 3, (1, 1, 1, 1), True)),      # TF32: three 32-channel groups; F32X3: gather kernel
+    ("kernel_5x5_cin64", (1, 64, 40, 44, 32, 5, 5, (2, 2, 2, 2), False)),
+    ("uneven_pads_cin128", (2, 128, 33, 50, 16, 3, 3, (0, 2, 1, 0), False)),
+])
+def test_window_kernel_float32_modes(dev, window_path, label, shape):
+    """F32X3 mode is the float32 product: the float32 gate against the oracle.  TF32 mode truncates the activations
+    to tf32 and rounds the weights to the nearest tf32, then accumulates in float32: the float32 gate against the
+    oracle on those operands.  The gather kernel must agree with each at its own gate."""
+    from oracle import conv2d_c
+
+    torch, ops, device = dev
+    n, cin, h, w_, cout, kh, kw, pads, relu = shape
+    rng = np.random.default_rng(zlib.crc32(label.encode()) + 1)
+    x = rng.standard_normal((n, cin, h, w_)).astype(np.float32)
+    w = (rng.standard_normal((cout, cin, kh, kw)) * np.sqrt(2.0 / (kh * kw * cin))).astype(np.float32)
+    b = rng.standard_normal(cout).astype(np.float32)
+    c = {"X": x, "W": w, "bias": b, "attrs": np.asarray([1, 1, *pads, 1, 1, 1, int(relu)], np.int32)}
+    exact = conv2d_c(x, w, b, pads=pads, relu=relu)
+    tf32 = conv2d_c(_tf32_truncate(x), _tf32_round_nearest(w), b, pads=pads, relu=relu)
+    window_path(1)
+    assert_fp32_gate(_run_conv(dev, c, "f32x3").cpu().numpy(), exact, f"{label} f32x3 window kernel")
+    assert_fp32_gate(_run_conv(dev, c, "tf32").cpu().numpy(), tf32, f"{label} tf32 window kernel")
+    if pads[0] == pads[2] and pads[1] == pads[3]:
+        geo = ops.native.dcnv2_launch_geometry(n, cin, h, w_, cout, kh, kw, (1, 1), pads[:2], (1, 1), 1, 1,
+                                               ops.native.DCN_TF32, plain=True)
+        assert geo.kernel == b"conv_window_kernel<tf32>"
+    window_path(0)
+    assert_fp32_gate(_run_conv(dev, c, "f32x3").cpu().numpy(), exact, f"{label} f32x3 gather kernel")
+    assert_rel_gate(_run_conv(dev, c, "tf32").cpu().numpy(), exact, 1e-2, f"{label} tf32 gather kernel")
 
 
 def test_window_kernel_split_outputs_sharding_and_weight_reuse(dev, window_path):

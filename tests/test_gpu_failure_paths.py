@@ -102,7 +102,7 @@ def test_expired_wait_in_the_window_kernel_of_plain_convolutions(dev, fault_buil
     x = rng.standard_normal((2, 64, 40, 30)).astype(np.float32)
     w = (rng.standard_normal((27, 64, 3, 3)) * 0.05).astype(np.float32)
     geo = native.dcnv2_launch_geometry(2, 64, 40, 30, 27, 3, 3, (1, 1), (1, 1), (1, 1), 1, 1, native.DCN_BF16, plain=True)
-    assert geo.kernel == b"conv_window_kernel"
+    assert geo.kernel == b"conv_window_kernel<bf16>"
     xd, wd = torch.from_numpy(x).to(device), torch.from_numpy(w).to(device)
     status = torch.zeros(1, dtype=torch.int32, device=device)
     ops.conv2d_forward(xd, wd, None, pads=(1, 1, 1, 1), math="bf16", status_word=status,

@@ -203,19 +203,20 @@ def test_launch_geometry_follows_the_kernel_dispatch_rules():
 
     tiny = native.dcnv2_launch_geometry(1, 8, 5, 5, 8, 3, 3, (1, 1), (1, 1), (1, 1), 1, 1, native.DCN_BF16)
     assert tiny.kernel == b"dcn_direct_kernel" and tuple(tiny.block) == (256, 1, 1) and tuple(tiny.grid) == (1, 1, 1)
-    # BF16 conv_offset: the persistent window kernel, one CTA per SM over 6 * 13 * 4 tiles of 16 x 8 pixels
-    conv = native.dcnv2_launch_geometry(6, 256, 58, 100, 27, 3, 3, (1, 1), (1, 1), (1, 1), 1, 1, native.DCN_BF16, plain=True)
-    assert conv.kernel == b"conv_window_kernel" and tuple(conv.block) == (544, 1, 1) and tuple(conv.grid) == (148, 1, 1)
-    assert conv.dynamic_smem_bytes <= 227 * 1024
+    # conv_offset: the persistent window kernel in every math mode, one CTA per SM over 6 * 13 * 4 tiles of 16 x 8 pixels
+    for mode, name in ((native.DCN_BF16, b"bf16"), (native.DCN_TF32, b"tf32"), (native.DCN_F32X3, b"f32x3")):
+        conv = native.dcnv2_launch_geometry(6, 256, 58, 100, 27, 3, 3, (1, 1), (1, 1), (1, 1), 1, 1, mode, plain=True)
+        assert conv.kernel == b"conv_window_kernel<" + name + b">" and tuple(conv.block) == (544, 1, 1)
+        assert tuple(conv.grid) == (148, 1, 1) and conv.dynamic_smem_bytes <= 227 * 1024
     few = native.dcnv2_launch_geometry(1, 256, 58, 100, 27, 3, 3, (1, 1), (1, 1), (1, 1), 1, 1, native.DCN_BF16, plain=True)
-    assert few.kernel == b"conv_window_kernel" and tuple(few.grid) == (52, 1, 1)
-    # other math modes keep the gather kernel: two CTAs per SM beyond one wave, the wide shape within one wave
-    conv = native.dcnv2_launch_geometry(6, 256, 58, 100, 27, 3, 3, (1, 1), (1, 1), (1, 1), 1, 1, native.DCN_TF32, plain=True)
+    assert few.kernel == b"conv_window_kernel<bf16>" and tuple(few.grid) == (52, 1, 1)
+    # what does not qualify keeps the gather kernel: two CTAs per SM beyond one wave, the wide shape within one wave
+    conv = native.dcnv2_launch_geometry(6, 256, 58, 100, 27, 3, 3, (1, 1), (2, 2), (2, 2), 1, 1, native.DCN_TF32, plain=True)
     assert conv.kernel == b"dcn_umma_kernel<tf32,plain,narrow>" and tuple(conv.block) == (352, 1, 1)
-    one_wave = native.dcnv2_launch_geometry(3, 256, 58, 100, 27, 3, 3, (1, 1), (1, 1), (1, 1), 1, 1, native.DCN_TF32, plain=True)
+    one_wave = native.dcnv2_launch_geometry(3, 256, 58, 100, 27, 3, 3, (1, 1), (2, 2), (2, 2), 1, 1, native.DCN_TF32, plain=True)
     assert one_wave.kernel == b"dcn_umma_kernel<tf32,plain,wide>" and tuple(one_wave.grid) == (136, 1, 1)
-    strided = native.dcnv2_launch_geometry(6, 256, 58, 100, 27, 3, 3, (2, 2), (1, 1), (1, 1), 1, 1, native.DCN_BF16, plain=True)
-    assert strided.kernel.startswith(b"dcn_umma_kernel<bf16,plain")
+    wide_out = native.dcnv2_launch_geometry(6, 256, 58, 100, 48, 3, 3, (1, 1), (1, 1), (1, 1), 1, 1, native.DCN_F32X3, plain=True)
+    assert wide_out.kernel.startswith(b"dcn_umma_kernel<f32x3,plain")       # F32X3 windows stop at 32 output channels
     c5 = native.dcnv2_launch_geometry(6, 512, 29, 50, 512, 3, 3, (1, 1), (1, 1), (1, 1), 1, 1, native.DCN_F32X3)
     assert tuple(c5.grid) == (68, 2, 1) and c5.dynamic_smem_bytes <= 227 * 1024
     odd = native.msda_launch_geometry(native.GACB_F32, [(3, 5)], 2, 7, 3, 6, 2)
