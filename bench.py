@@ -379,7 +379,17 @@ def bench_dcn(device, keys=("dcn_c4", "dcn_c5"), modes=("f32x3", "tf32", "bf16")
                                       dilation=wl.dilation, math=math, out=y, workspace=ws, status_word=status, stream=stream,
                                       reuse_weights=True)
 
+                def conv_offset_gather_kernel():
+                    # the same call with the window kernel switched off: the gather kernel on integer taps
+                    before = ops.native.load().gacb_conv_window_path(0)
+                    try:
+                        conv_offset()
+                    finally:
+                        ops.native.load().gacb_conv_window_path(before)
+
                 for name, fn, flops in (("conv_offset", conv_offset, 2.0 * wl.batch * 3 * k2 * wl.cin * k2 * ho * wo),
+                                        ("conv_offset/gather_kernel", conv_offset_gather_kernel,
+                                         2.0 * wl.batch * 3 * k2 * wl.cin * k2 * ho * wo),
                                         ("conv_offset+dcn+bn+relu", chain, None),
                                         ("conv_offset+dcn+bn+relu/weights_prepacked", chain_steady, None),
                                         ("conv_offset+dcn+bn+relu/shared_input_copy", chain_shared, None),
@@ -898,9 +908,22 @@ def main() -> None:
         for label, mode, storage in (("broadcast_f32", "broadcast", "float32"), ("all_gather_f32", "all_gather", "float32"),
                                      ("all_gather_bf16", "all_gather", "bfloat16"), ("peer_copy_f32", "peer_copy", "float32"),
                                      ("peer_copy_bf16", "peer_copy", "bfloat16")):
-            runner = ShardedMsda(batch=workload.batch, spatial_shapes=workload.spatial_shapes, queries=workload.queries,
-                                 heads=workload.heads, head_dim=workload.head_dim, points=workload.points, device=device,
-                                 value_storage=storage, replicate=mode)
+            # Setting up the peer-copy route maps every other rank's buffers (CUDA IPC); if that fails on any rank, all
+            # ranks leave the route out together and the line says why, instead of losing the whole bench line.
+            failure = ""
+            try:
+                runner = ShardedMsda(batch=workload.batch, spatial_shapes=workload.spatial_shapes, queries=workload.queries,
+                                     heads=workload.heads, head_dim=workload.head_dim, points=workload.points, device=device,
+                                     value_storage=storage, replicate=mode)
+            except Exception as exc:  # noqa: BLE001 - reported in the line
+                if mode != "peer_copy":
+                    raise
+                runner, failure = None, f"{type(exc).__name__}: {exc}"
+            ok = torch.tensor([0 if failure else 1], device=device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if int(ok.item()) == 0:
+                replication[label] = {"unavailable": failure or "setup failed on another rank"}
+                continue      # what was set up is left to process exit: closing it needs every rank
             runner.load_host(full_host["value"], full_host["sampling_locations"], full_host["attention_weights"])
             runner.upload()
             if mode == "broadcast":
@@ -933,8 +956,14 @@ def main() -> None:
                 sharded_e2e = {"ms": ms, "h2d": runner.h2d_bytes, "d2h": runner.d2h_bytes,
                                "out": e2e_out_t.numpy().copy()}
             if mode == "peer_copy":
-                # the device-side barriers never gave up, and the slabs the copy engines assembled give the oracle's result
-                runner.peers.check()
+                # the device-side barriers never gave up (on any rank), and the slabs the copy engines assembled give
+                # the oracle's result
+                word = torch.tensor([int(runner.peers.status.item())], device=device)
+                dist.all_reduce(word, op=dist.ReduceOp.MAX)
+                if int(word.item()) != 0:
+                    replication[label] = {"unavailable": f"a device-side peer barrier ran out (status {int(word.item())})"}
+                    runner.close()
+                    continue
                 got = runner.out[:, :8].cpu().numpy()
                 from oracle import msda_c
 

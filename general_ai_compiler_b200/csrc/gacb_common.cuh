@@ -111,7 +111,5 @@ __device__ __forceinline__ void async_copy_16(uint32_t dst, const void *src) {
 }
 __device__ __forceinline__ void async_copy_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void async_copy_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
-// Wait until at most the newest committed group is still in flight.
-__device__ __forceinline__ void async_copy_wait_all_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 
 }  // namespace gacb
