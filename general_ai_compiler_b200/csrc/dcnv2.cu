@@ -49,6 +49,8 @@
 //    Every mbarrier wait is bounded: on expiry the kernel raises a shared abort
 //    flag, sets the caller's status word, drains what it issued, frees TMEM and
 //    returns.
+#include <cuda.h>   // CUtensorMap and its enums only; the encoder is looked up through the runtime
+
 #include <algorithm>
 #include <atomic>
 #include <mutex>
@@ -1237,25 +1239,35 @@ __global__ void __launch_bounds__(CtaShape<NARROW>::kThreads, CtaShape<NARROW>::
 //   F32X3  two windows made by the fill from the float32 copy, hi = bf16(x) and lo = bf16(x - hi), and three
 //          products per slice, hi*Whi into a main accumulator, lo*Whi + hi*Wlo into a cross accumulator: the gather
 //          kernel's arithmetic.
+// In BF16 and TF32 mode nothing touches the texels on their way, so ONE thread brings a window with tensor copies
+// (TMA, cp.async.bulk.tensor; zero fill outside the image comes with it) and the fill warps are not launched.  The
+// window then has the tensor copy's 128-byte-swizzled K-major layout: a texel is one 128-byte row (8 chunks, XOR-ed
+// with the row's position in its 1 KB), the texels of the window follow each other densely, 16 chunks of channels
+// are two such sub-windows.  The swizzle is a function of the shared-memory ADDRESS (measured: a descriptor whose
+// start address is any multiple of 128 bytes, with a stride between 8-row groups that is no multiple of 1 KB, and
+// base offset 0, reads the right rows; filling in the base offset gives wrong ones), so the shifted views work
+// exactly as in the un-swizzled layout: start address + (ky * window width + kx) * 128.
 template <int MODE>
 struct WinTraits;
+// kTma: the windows are brought by tensor copies (TMA) in the 128-byte-swizzled layout; otherwise eight warps make
+// them (F32X3: the float32 texels have to be split into bf16 pairs on the way) in the un-swizzled chunked layout.
 template <>
 struct WinTraits<MODE_BF16> {
   using Xt = __nv_bfloat16;
   static constexpr int kChunkCh = 8, kParts = 1;
-  static constexpr bool kTf32 = false;
+  static constexpr bool kTf32 = false, kTma = true;
 };
 template <>
 struct WinTraits<MODE_TF32> {
   using Xt = float;
   static constexpr int kChunkCh = 4, kParts = 1;
-  static constexpr bool kTf32 = true;
+  static constexpr bool kTf32 = true, kTma = true;
 };
 template <>
 struct WinTraits<MODE_F32X3> {
   using Xt = float;
   static constexpr int kChunkCh = 8, kParts = 2;
-  static constexpr bool kTf32 = false;
+  static constexpr bool kTf32 = false, kTma = false;
 };
 __host__ __device__ inline int win_chunk_channels(int mode) { return mode == MODE_TF32 ? 4 : 8; }
 constexpr int kWinTileH = 16, kWinTileW = 8;          // pixels of a tile: 16 rows x 8 columns = 128 MMA rows
@@ -1286,6 +1298,8 @@ struct ConvWinArgs {
   unsigned b_stage_bytes;
   int tmem_cols;
   int drop_weight_copies;       // test build only (GACB_DCN_FAULT_INJECT): the loader skips every copy
+  // TMA windows (BF16 and TF32): a tensor copy brings a box of {128 bytes of channels, win_w texels, win_h rows}
+  unsigned tma_sub_bytes;       // bytes from the sub-window of channels [0, 8 chunks) to that of the next 8 chunks
 };
 
 // Un-swizzled K-major operand: core matrices of 8 rows x 16 bytes, `lbo` bytes between the two core matrices an MMA
@@ -1297,6 +1311,26 @@ __device__ __forceinline__ uint64_t umma_smem_desc_plain(uint32_t smem_addr, uin
   d |= (uint64_t)((sbo >> 4) & 0x3FFFu) << 32;
   d |= (uint64_t)1 << 46;                              // descriptor version of sm_100; layout type 0 = no swizzle
   return d;
+}
+
+// K-major operand in the 128-byte swizzle whose first row may start at any multiple of 128 bytes: rows of 128
+// bytes, `sbo` bytes (any multiple of 128) between 8-row groups.
+__device__ __forceinline__ uint64_t umma_smem_desc_sw128_at(uint32_t smem_addr, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;                              // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)((sbo >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;                              // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                              // SWIZZLE_128B; base offset 0: the swizzle follows the address
+  return d;
+}
+// One tiled tensor copy global -> this CTA's shared memory (4-D map); completion is counted in bytes on `bar`.
+// No cluster multicast.
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, int c3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+      : "memory");
 }
 
 template <int MODE>
@@ -1323,11 +1357,11 @@ __global__ void __launch_bounds__(256) conv_window_pack_weights(const float *__r
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(kWinThreads, 1) conv_window_kernel(const __grid_constant__ ConvWinArgs u) {
+__global__ void __launch_bounds__(kWinThreads, 1) conv_window_kernel(const __grid_constant__ ConvWinArgs u, const __grid_constant__ CUtensorMap xt_map) {
   using T = WinTraits<MODE>;
   using Xt = typename T::Xt;
   extern __shared__ unsigned char smem_raw[];
-  unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~(uintptr_t)127);
+  unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const DcnArgs &a = u.d;
   unsigned char *windows = smem;
   unsigned char *b_ring = smem + (size_t)u.win_bufs * u.win_bytes;
@@ -1352,7 +1386,7 @@ __global__ void __launch_bounds__(kWinThreads, 1) conv_window_kernel(const __gri
   const int tiles_per_image = u.tiles_x * u.tiles_y;
   if (tid == 0) {
     for (int i = 0; i < kWinMaxBufs; ++i) {
-      mbar_init(win_full(i), kWinFillWarps);
+      mbar_init(win_full(i), T::kTma ? 1 : kWinFillWarps);
       mbar_init(win_empty(i), kWinAccs);      // one commit per issuing thread
     }
     for (int i = 0; i < kWinMaxBStages; ++i) {
@@ -1376,35 +1410,62 @@ __global__ void __launch_bounds__(kWinThreads, 1) conv_window_kernel(const __gri
   const int set_cols = T::kParts * kWinAccs * u.n_pad;      // tensor-memory columns of one tile's accumulators
 
   if (warp >= kWinFirstFillWarp) {
-    // ------------------------------------------------------------------ window fill (eight warps)
-    // A thread copies the 16-byte pieces (texel, chunk) with chunk = ft % chunks (neighbouring lanes read one texel's
-    // channels) and texel = ft / chunks, + 256 / chunks, ...; chunks is 8 or 16, so nothing below divides.
-    const int ft = tid - kWinFirstFillWarp * 32;                    // 0 .. 255
-    const int chunks = u.chunks, chunk_shift = chunks == 16 ? 4 : 3;
-    const int c = ft & (chunks - 1), tt0 = ft >> chunk_shift, tt_step = (kWinFillWarps * 32) >> chunk_shift;
-    const int wy0 = tt0 / u.win_w, wx0 = tt0 - wy0 * u.win_w;
-    bool alive = true;
-    int buf = 0, round = 0;                                         // ring position: step % win_bufs, step / win_bufs
-    for (int t = blockIdx.x; t < u.tiles_total; t += gridDim.x) {
-      const int img = t / tiles_per_image, r = t - img * tiles_per_image;
-      const int ty = r / u.tiles_x, tx = r - ty * u.tiles_x;
-      const int y0 = ty * kWinTileH - a.ph, x0 = tx * kWinTileW - a.pw;     // input position of window texel (0, 0)
-      const Xt *image = static_cast<const Xt *>(u.xt) + (size_t)img * a.H * a.W * a.Cin;
-      for (int cg = 0; cg < u.cgroups; ++cg) {
-        if (alive) alive = mbar_wait_warp(win_empty(buf), (round & 1) ^ 1, abort_flag, lane);
-        if (alive) {
-          unsigned char *win = windows + (size_t)buf * u.win_bytes;
-          unsigned char *dst = win + (size_t)c * u.chunk_stride + (size_t)tt0 * 16;
-          const Xt *src = image + cg * u.cg_channels + c * T::kChunkCh;
-          int wy = wy0, wx = wx0;
-          for (int tt = tt0; tt < u.win_texels; tt += tt_step, dst += tt_step * 16) {
-            const int gy = y0 + wy, gx = x0 + wx;
-            const bool inside = gy >= 0 && gy < a.H && gx >= 0 && gx < a.W;
-            const int e = inside ? (int)GACB_INDEX((gy * a.W + gx) * a.Cin, (long long)a.H * a.W * a.Cin, 12) : 0;
-            if constexpr (T::kParts == 2) {
-              // eight float32 channels -> bf16 hi and lo pieces of the two windows
-              uint4 hi = make_uint4(0u, 0u, 0u, 0u), lo = hi;
-              if (inside) {
+    if constexpr (T::kTma) {
+      // ---------------------------------------------------------------- window fill by tensor copies (one thread)
+      if (warp == kWinFirstFillWarp && lane == 0) {
+        const int subs = u.chunks / 8;                         // one tensor copy per 128 bytes of channels
+        int buf = 0, round = 0, issued = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < u.tiles_total && ok; t += gridDim.x) {
+          const int img = t / tiles_per_image, r = t - img * tiles_per_image;
+          const int ty = r / u.tiles_x, tx = r - ty * u.tiles_x;
+          const int y0 = ty * kWinTileH - a.ph, x0 = tx * kWinTileW - a.pw;   // may be negative: the copy fills zeros there
+          for (int cg = 0; cg < u.cgroups; ++cg) {
+            if (!mbar_wait(win_empty(buf), (round & 1) ^ 1, abort_flag)) { ok = false; break; }
+            mbar_arrive_expect_tx(win_full(buf), (uint32_t)subs * 128u * (uint32_t)u.win_texels);
+            for (int sub = 0; sub < subs; ++sub)
+              tma_load_4d(smem_u32(windows + (size_t)buf * u.win_bytes + (size_t)sub * u.tma_sub_bytes), &xt_map,
+                          cg * u.cg_channels + sub * 8 * T::kChunkCh, x0, y0, img, win_full(buf));
+            ++issued;
+            if (++buf == u.win_bufs) { buf = 0; ++round; }
+          }
+        }
+        if (*abort_flag && issued > 0) {
+          // drain: every copy issued must have landed before shared memory is released (as in the weight loader)
+          for (int back = 1; back <= u.win_bufs && back <= issued; ++back) {
+            int pb = buf - back, pr = round;
+            if (pb < 0) { pb += u.win_bufs; --pr; }
+            for (uint32_t poll = 0; poll < kSpinLimit && !mbar_try_wait(win_full(pb), pr & 1); ++poll) {
+            }
+          }
+        }
+      }
+    } else {
+      // ---------------------------------------------------------------- window fill (eight warps), F32X3
+      // A thread makes the 16-byte pieces (texel, chunk) with chunk = ft % 8 (neighbouring lanes read one texel's
+      // channels) and texel = ft / 8, + 32, ...: eight float32 channels become a bf16 hi piece and a bf16 lo piece.
+      const int ft = tid - kWinFirstFillWarp * 32;                    // 0 .. 255
+      const int c = ft & 7, tt0 = ft >> 3, tt_step = (kWinFillWarps * 32) >> 3;
+      const int wy0 = tt0 / u.win_w, wx0 = tt0 - wy0 * u.win_w;
+      bool alive = true;
+      int buf = 0, round = 0;                                         // ring position: step % win_bufs, step / win_bufs
+      for (int t = blockIdx.x; t < u.tiles_total; t += gridDim.x) {
+        const int img = t / tiles_per_image, r = t - img * tiles_per_image;
+        const int ty = r / u.tiles_x, tx = r - ty * u.tiles_x;
+        const int y0 = ty * kWinTileH - a.ph, x0 = tx * kWinTileW - a.pw;     // input position of window texel (0, 0)
+        const Xt *image = static_cast<const Xt *>(u.xt) + (size_t)img * a.H * a.W * a.Cin;
+        for (int cg = 0; cg < u.cgroups; ++cg) {
+          if (alive) alive = mbar_wait_warp(win_empty(buf), (round & 1) ^ 1, abort_flag, lane);
+          if (alive) {
+            unsigned char *win = windows + (size_t)buf * u.win_bytes;
+            unsigned char *dst = win + (size_t)c * u.chunk_stride + (size_t)tt0 * 16;
+            const Xt *src = image + cg * u.cg_channels + c * T::kChunkCh;
+            int wy = wy0, wx = wx0;
+            for (int tt = tt0; tt < u.win_texels; tt += tt_step, dst += tt_step * 16) {
+              const int gy = y0 + wy, gx = x0 + wx;
+              uint4 hi = make_uint4(0u, 0u, 0u, 0u), lo = hi;         // zero padding outside the image
+              if (gy >= 0 && gy < a.H && gx >= 0 && gx < a.W) {
+                const int e = (int)GACB_INDEX((gy * a.W + gx) * a.Cin, (long long)a.H * a.W * a.Cin, 12);
                 const float4 v0 = __ldg(reinterpret_cast<const float4 *>(src + e));
                 const float4 v1 = __ldg(reinterpret_cast<const float4 *>(src + e) + 1);
                 const float x[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
@@ -1412,36 +1473,25 @@ __global__ void __launch_bounds__(kWinThreads, 1) conv_window_kernel(const __gri
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                   const __nv_bfloat16 h0 = __float2bfloat16_rn(x[2 * k]), h1 = __float2bfloat16_rn(x[2 * k + 1]);
-                  const __nv_bfloat16 l0 = __float2bfloat16_rn(x[2 * k] - __bfloat162float(h0));
-                  const __nv_bfloat16 l1 = __float2bfloat16_rn(x[2 * k + 1] - __bfloat162float(h1));
-                  h[k] = (uint32_t)__bfloat16_as_ushort(h0) | ((uint32_t)__bfloat16_as_ushort(h1) << 16);
-                  l[k] = (uint32_t)__bfloat16_as_ushort(l0) | ((uint32_t)__bfloat16_as_ushort(l1) << 16);
+                  h[k] = pack_bf16x2(h0, h1);
+                  l[k] = pack_bf16x2(__float2bfloat16_rn(x[2 * k] - __bfloat162float(h0)),
+                                     __float2bfloat16_rn(x[2 * k + 1] - __bfloat162float(h1)));
                 }
                 hi = make_uint4(h[0], h[1], h[2], h[3]);
                 lo = make_uint4(l[0], l[1], l[2], l[3]);
               }
               *reinterpret_cast<uint4 *>(dst) = hi;
               *reinterpret_cast<uint4 *>(dst + u.win_part_bytes) = lo;
-            } else if (inside) {
-              async_copy_16(smem_u32(dst), src + e);
-            } else {
-              *reinterpret_cast<uint4 *>(dst) = make_uint4(0u, 0u, 0u, 0u);   // zero padding
+              wx += tt_step;
+              while (wx >= u.win_w) { wx -= u.win_w; ++wy; }
             }
-            wx += tt_step;
-            while (wx >= u.win_w) { wx -= u.win_w; ++wy; }
+            fence_proxy_async_smem();      // generic-proxy writes -> visible to the tensor core's async proxy
           }
-          if constexpr (T::kParts == 1) {
-            // Handing a window over only after the next one's copies were issued (two copy groups in flight) was
-            // measured slower: 27.5 against 26.0 us on the c4 shape.
-            async_copy_commit();
-            async_copy_wait_all();
-          }
-          fence_proxy_async_smem();      // generic-proxy writes -> visible to the tensor core's async proxy
+          // one arrival per warp, after every lane's writes are fenced
+          const bool warp_alive = __all_sync(0xffffffffu, alive);
+          if (warp_alive && lane == 0) mbar_arrive(win_full(buf));
+          if (++buf == u.win_bufs) { buf = 0; ++round; }
         }
-        // one arrival per warp, after every lane's writes are fenced
-        const bool warp_alive = __all_sync(0xffffffffu, alive);
-        if (warp_alive && lane == 0) mbar_arrive(win_full(buf));
-        if (++buf == u.win_bufs) { buf = 0; ++round; }
       }
     }
   } else if (warp == kWinLoaderWarp) {
@@ -1481,12 +1531,15 @@ __global__ void __launch_bounds__(kWinThreads, 1) conv_window_kernel(const __gri
     {
       const int issuer = __shfl_sync(0xffffffffu, warp - kWinMmaWarp, 0);   // takes the slices issuer, issuer + kWinAccs, ...
       const uint32_t idesc = umma_idesc(T::kTf32 ? 2 : 1, kTileM, u.n_pad);
-      const uint32_t a_lbo = (uint32_t)u.chunk_stride, a_sbo = (uint32_t)u.win_w * 16u;
+      constexpr bool tma = T::kTma;
+      // bytes from a texel to the next one, and texels per window row, in the window's layout
+      const uint32_t texel_bytes = tma ? 128u : 16u, row_texels = (uint32_t)u.win_w;
+      const uint32_t a_lbo = (uint32_t)u.chunk_stride, a_sbo = row_texels * texel_bytes;
       const uint32_t b_lbo = (uint32_t)u.n_pad * 16u, b_sbo = 128u;
       // descriptors with a zero start address; a start address is added in 16-byte units
       const uint64_t a_desc0 = umma_smem_desc_plain(0, a_lbo, a_sbo), b_desc0 = umma_smem_desc_plain(0, b_lbo, b_sbo);
       // one slice = the two chunks an MMA reads along K (16 channels, 8 in TF32 mode), in 16-byte units
-      const uint32_t a_k16 = (2u * a_lbo) >> 4, b_k16 = (2u * b_lbo) >> 4;
+      const uint32_t a_k16 = tma ? 2u : (2u * a_lbo) >> 4, b_k16 = (2u * b_lbo) >> 4;   // TMA rows: 32 bytes along the row
       const int k16_quads = u.chunks / (2 * kWinAccs);
       const uint32_t a_lo = u.win_part_bytes >> 4, b_lo = u.kp_part_bytes >> 4;     // F32X3: from the hi part to the lo part
       const uint32_t windows_addr = smem_u32(windows), ring_addr = smem_u32(b_ring);
@@ -1509,7 +1562,10 @@ __global__ void __launch_bounds__(kWinThreads, 1) conv_window_kernel(const __gri
             const int k1 = min(K, k0 + u.stage_kps);
             uint64_t bd = b_desc0 + (uint64_t)((ring_addr + (uint32_t)s * u.b_stage_bytes) >> 4) + issuer * b_k16;
             for (int kp = k0; kp < k1; ++kp) {
-              uint64_t ad = a_desc0 + (uint64_t)((win + (uint32_t)(ky * u.win_w + kx) * 16u) >> 4) + issuer * a_k16;
+              const uint32_t tap = win + ((uint32_t)ky * row_texels + (uint32_t)kx) * texel_bytes;   // first row of this kernel point
+              // TMA layout: the q-th group of kWinAccs slices is the q-th sub-window; chunked layout: 2 * kWinAccs chunks on
+              uint64_t ad = (tma ? umma_smem_desc_sw128_at(tap, a_sbo) : a_desc0 + (uint64_t)(tap >> 4)) + issuer * a_k16;
+              const uint32_t a_next = tma ? (u.tma_sub_bytes >> 4) : kWinAccs * a_k16;
               for (int q = 0; q < k16_quads; ++q) {
                 if (elect_one()) {
                   umma_ss<T::kTf32>(acc, ad, bd, idesc, accumulate);
@@ -1519,7 +1575,7 @@ __global__ void __launch_bounds__(kWinThreads, 1) conv_window_kernel(const __gri
                   }
                 }
                 accumulate = 1u;
-                ad += kWinAccs * a_k16;
+                ad += a_next;
                 bd += kWinAccs * b_k16;      // after the last slice of a kernel point: the next point's first slice
               }
               if constexpr (T::kParts == 2) bd += b_lo;   // ... which lies behind this point's lo part
@@ -1619,7 +1675,11 @@ __global__ void __launch_bounds__(kWinThreads, 1) conv_window_kernel(const __gri
 // 0 = plain convolutions always take the gather kernel; 1 (default) = the window kernel where it applies.
 std::atomic<int> g_conv_window_path{1};
 
+
 // Does the window kernel apply, and with which shape?  (Plain convolution over whole images.)
+// Threads of a launch: with tensor copies only the first of the fill warps is needed.
+inline int win_threads(int mode) { return parts_of(mode) == 1 ? (kWinFirstFillWarp + 1) * 32 : kWinThreads; }
+
 bool plan_conv_window(const DcnArgs &a, int mode, size_t blob_capacity, ConvWinArgs &u, size_t &smem) {
   if (!g_conv_window_path.load(std::memory_order_relaxed)) return false;
   const bool whole = a.m_first == 0 && a.row_begin == 0 && a.row_end == a.Ho &&
@@ -1632,14 +1692,19 @@ bool plan_conv_window(const DcnArgs &a, int mode, size_t blob_capacity, ConvWinA
   if ((long long)(a.n_end - a.n_begin) * a.H * a.W * a.Cin > 2147483647LL) return false;
   const int K = a.Kh * a.Kw;
   u.n_pad = (a.Cout + 31) / 32 * 32;
-  u.chunks = (parts == 1 && a.Cin % (16 * chunk_ch) == 0) ? 16 : 8;
-  u.cg_channels = u.chunks * chunk_ch;
-  u.cgroups = a.Cin / u.cg_channels;
   u.win_h = kWinTileH + a.Kh - 1;
   u.win_w = kWinTileW + a.Kw - 1;
   u.win_texels = u.win_h * u.win_w;
+  const bool tma = parts == 1;       // WinTraits<mode>::kTma
+  if (tma && (u.win_w > 256 || u.win_h > 256)) return false;      // box limits of a tensor copy
+  u.chunks = (parts == 1 && a.Cin % (16 * chunk_ch) == 0) ? 16 : 8;
+  u.cg_channels = u.chunks * chunk_ch;
+  u.cgroups = a.Cin / u.cg_channels;
   u.chunk_stride = (u.win_texels | 1) * 16;
-  u.win_part_bytes = (unsigned)(((size_t)u.chunks * u.chunk_stride + 127) / 128 * 128);
+  // TMA layout: one sub-window of 128-byte texel rows per 8 chunks, each starting at a multiple of 1024 bytes
+  u.tma_sub_bytes = (unsigned)((128 * u.win_texels + 1023) / 1024 * 1024);
+  u.win_part_bytes = tma ? (unsigned)(u.chunks / 8) * u.tma_sub_bytes
+                           : (unsigned)(((size_t)u.chunks * u.chunk_stride + 127) / 128 * 128);
   u.win_bytes = (unsigned)parts * u.win_part_bytes;
   u.kp_part_bytes = (unsigned)((size_t)u.chunks * u.n_pad * 16);
   u.kp_bytes = (unsigned)parts * u.kp_part_bytes;
@@ -1649,7 +1714,7 @@ bool plan_conv_window(const DcnArgs &a, int mode, size_t blob_capacity, ConvWinA
   if ((size_t)u.cgroups * K * u.kp_bytes > blob_capacity) return false;
   // the un-swizzled descriptor's offsets are 14-bit counts of 16 bytes
   if ((size_t)u.chunk_stride >= (1u << 18) || (size_t)u.n_pad * 16 >= (1u << 18)) return false;
-  const size_t fixed = 128 /*alignment*/ + (2 * kWinMaxBufs + 2 * kWinMaxBStages + 4 + kWinAccs) * 8 + 16 + 64 * sizeof(float);
+  const size_t fixed = 1024 /*alignment*/ + (2 * kWinMaxBufs + 2 * kWinMaxBStages + 4 + kWinAccs) * 8 + 16 + 64 * sizeof(float);
   const size_t budget = 227 * 1024;
   u.win_bufs = 3;
   while (u.win_bufs > 2 && fixed + (size_t)u.win_bufs * u.win_bytes + 3 * (size_t)u.b_stage_bytes > budget) --u.win_bufs;
@@ -1682,6 +1747,35 @@ int launch_conv_window(const DcnArgs &a, ConvWinArgs &u, size_t smem, const void
   u.blob = blob;
   u.status = status;
   u.drop_weight_copies = (reuse_flags & kTestDropWeightCopies) ? 1 : 0;
+  CUtensorMap xt_map{};
+  if (WinTraits<MODE>::kTma) {
+    // X_t as a 4-D tensor (channels, width, height, image), innermost first; a box is one window of one channel group
+    using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static std::atomic<EncodeFn> encode{nullptr};
+    EncodeFn fn = encode.load();
+    if (!fn) {
+      void *sym = nullptr;
+      cudaDriverEntryPointQueryResult found;
+      const int rc = check_cuda(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &found),
+                                "cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)");
+      if (rc != GACB_OK) return rc;
+      if (found != cudaDriverEntryPointSuccess || !sym)
+        return fail(GACB_ERR_UNSUPPORTED, "conv2d: the driver does not provide cuTensorMapEncodeTiled");
+      fn = reinterpret_cast<EncodeFn>(sym);
+      encode.store(fn);
+    }
+    const cuuint64_t es = WinTraits<MODE>::kTf32 ? 4 : 2;
+    const cuuint64_t dims[4] = {(cuuint64_t)a.Cin, (cuuint64_t)a.W, (cuuint64_t)a.H, (cuuint64_t)(a.n_end - a.n_begin)};
+    const cuuint64_t strides[3] = {(cuuint64_t)a.Cin * es, (cuuint64_t)a.W * a.Cin * es, (cuuint64_t)a.H * a.W * a.Cin * es};
+    const cuuint32_t box[4] = {(cuuint32_t)(8 * win_chunk_channels(MODE)), (cuuint32_t)u.win_w, (cuuint32_t)u.win_h, 1u};
+    const cuuint32_t unit[4] = {1u, 1u, 1u, 1u};
+    const CUresult res = fn(&xt_map, WinTraits<MODE>::kTf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+                            const_cast<void *>(xt), dims, strides, box, unit, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (res != CUDA_SUCCESS) return fail(GACB_ERR_CUDA, "conv2d: cuTensorMapEncodeTiled failed with %d", (int)res);
+  }
   static std::mutex attr_lock;      // one flag set per math mode (this function is a template)
   static bool attr_done[64] = {};
   {
@@ -1695,7 +1789,7 @@ int launch_conv_window(const DcnArgs &a, ConvWinArgs &u, size_t smem, const void
     }
   }
   const int grid = std::min(u.tiles_total, sms);
-  conv_window_kernel<MODE><<<grid, kWinThreads, smem, stream>>>(u);
+  conv_window_kernel<MODE><<<grid, win_threads(MODE), smem, stream>>>(u, xt_map);
   return check_cuda(cudaGetLastError(), "conv_window_kernel launch");
 }
 
@@ -2164,7 +2258,7 @@ GACB_API int gacb_dcnv2_launch_geometry(int n, int Cin, int H, int W, int Cout, 
   size_t cw_smem = 0;
   if (plan_conv_window(a, math_mode, p.blob_bytes, cw, cw_smem)) {
     out->grid[0] = std::min(cw.tiles_total, sm_count); out->grid[1] = out->grid[2] = 1;
-    out->block[0] = kWinThreads; out->block[1] = out->block[2] = 1;
+    out->block[0] = win_threads(math_mode); out->block[1] = out->block[2] = 1;
     out->dynamic_smem_bytes = cw_smem;
     out->units_per_cta = kTileM;      // per tile; a CTA takes tiles blockIdx.x, blockIdx.x + grid, ...
     snprintf(out->kernel, sizeof(out->kernel), "conv_window_kernel<%s>",

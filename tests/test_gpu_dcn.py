@@ -584,7 +584,7 @@ def test_window_kernel_matches_the_oracle_on_bf16_operands(dev, window_path, lab
     gathered = _run_conv(dev, c, "bf16").cpu().numpy()
     assert_fp32_gate(gathered, want, f"{label} gather kernel")
     if pads[0] == pads[2] and pads[1] == pads[3]:      # the geometry query takes symmetric pads
-        assert geo.kernel == b"conv_window_kernel<bf16>" and geo.block[0] == 544 and geo.grid[0] <= 148
+        assert geo.kernel == b"conv_window_kernel<bf16>" and geo.block[0] == 320 and geo.grid[0] <= 148
 
 
 def _tf32_truncate(a):

@@ -204,9 +204,10 @@ def test_launch_geometry_follows_the_kernel_dispatch_rules():
     tiny = native.dcnv2_launch_geometry(1, 8, 5, 5, 8, 3, 3, (1, 1), (1, 1), (1, 1), 1, 1, native.DCN_BF16)
     assert tiny.kernel == b"dcn_direct_kernel" and tuple(tiny.block) == (256, 1, 1) and tuple(tiny.grid) == (1, 1, 1)
     # conv_offset: the persistent window kernel in every math mode, one CTA per SM over 6 * 13 * 4 tiles of 16 x 8 pixels
-    for mode, name in ((native.DCN_BF16, b"bf16"), (native.DCN_TF32, b"tf32"), (native.DCN_F32X3, b"f32x3")):
+    # (tensor copies bring the windows in BF16 and TF32 mode: 10 warps; F32X3 launches eight fill warps more)
+    for mode, name, threads in ((native.DCN_BF16, b"bf16", 320), (native.DCN_TF32, b"tf32", 320), (native.DCN_F32X3, b"f32x3", 544)):
         conv = native.dcnv2_launch_geometry(6, 256, 58, 100, 27, 3, 3, (1, 1), (1, 1), (1, 1), 1, 1, mode, plain=True)
-        assert conv.kernel == b"conv_window_kernel<" + name + b">" and tuple(conv.block) == (544, 1, 1)
+        assert conv.kernel == b"conv_window_kernel<" + name + b">" and tuple(conv.block) == (threads, 1, 1)
         assert tuple(conv.grid) == (148, 1, 1) and conv.dynamic_smem_bytes <= 227 * 1024
     few = native.dcnv2_launch_geometry(1, 256, 58, 100, 27, 3, 3, (1, 1), (1, 1), (1, 1), 1, 1, native.DCN_BF16, plain=True)
     assert few.kernel == b"conv_window_kernel<bf16>" and tuple(few.grid) == (52, 1, 1)
