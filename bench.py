@@ -379,6 +379,13 @@ def bench_dcn(device, keys=("dcn_c4", "dcn_c5"), modes=("f32x3", "tf32", "bf16")
                                       dilation=wl.dilation, math=math, out=y, workspace=ws, status_word=status, stream=stream,
                                       reuse_weights=True)
 
+                def dcn_kernel_alone():
+                    # the tensor-core kernel by itself: weights packed and the channel-last copy already in the
+                    # workspace (as for the second call of the chain, which shares conv_offset's copy)
+                    ops.dcnv2_forward(t["X"], t["offset"], t["mask"], t["W"], t["bias"], stride=wl.stride, padding=wl.padding,
+                                      dilation=wl.dilation, math=math, out=y, workspace=ws, status_word=status, stream=stream,
+                                      reuse_weights=True, reuse_input=True)
+
                 def conv_offset_gather_kernel():
                     # the same call with the window kernel switched off: the gather kernel on integer taps
                     before = ops.native.load().gacb_conv_window_path(0)
@@ -394,7 +401,8 @@ def bench_dcn(device, keys=("dcn_c4", "dcn_c5"), modes=("f32x3", "tf32", "bf16")
                                         ("conv_offset+dcn+bn+relu/weights_prepacked", chain_steady, None),
                                         ("conv_offset+dcn+bn+relu/shared_input_copy", chain_shared, None),
                                         ("conv_offset+dcn+bn+relu/shared_input_copy+weights_prepacked", chain_shared_steady, None),
-                                        ("weights_prepacked", dcn_prepacked, float(wl.flops))):
+                                        ("weights_prepacked", dcn_prepacked, float(wl.flops)),
+                                        ("kernel_alone", dcn_kernel_alone, float(wl.flops))):
                     for _ in range(warmup):
                         fn()
                     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -410,6 +418,10 @@ def bench_dcn(device, keys=("dcn_c4", "dcn_c5"), modes=("f32x3", "tf32", "bf16")
                     entry = {"ms": ms}
                     if flops:
                         entry["tflops"] = flops / (ms * 1e-3) / 1e12
+                    if name == "kernel_alone":
+                        entry["frac_of_bf16_peak"] = entry["tflops"] / peak
+                        if math == "tf32":
+                            entry["frac_of_tf32_peak"] = entry["tflops"] / tf32_peak
                     out[f"{key}/{math}/{name}"] = entry
     return out
 
