@@ -1213,20 +1213,19 @@ __global__ void __launch_bounds__(CtaShape<NARROW>::kThreads, CtaShape<NARROW>::
 // Plain convolution with few output channels (the 27-channel conv_offset) from a staged input window
 // ----------------------------------------------------------------------------------------------
 // A plain stride-1 convolution gathers nothing: the A operand of kernel point (ky, kx) is the input window shifted
-// by (ky, kx).  A persistent CTA therefore stages, per 16 x 8 pixel tile and per group of 64 or 128 input channels,
-// the (16 + Kh - 1) x (8 + Kw - 1) window of the channel-last bf16 copy ONCE in shared memory, in the tensor core's
-// un-swizzled K-major layout [8-channel chunk][texel][8 channels] (a core matrix = eight consecutive texels of a
-// window row x 16 bytes), and issues one tcgen05.mma per (kernel point, 16 channels) whose A descriptor simply
-// starts (ky * window width + kx) texels further on: the eight pixels of a tile row are eight consecutive texels
-// (16 bytes apart), the next tile row is one window row further (the descriptor's stride byte offset), the next
-// 8-channel chunk one chunk stride further (its leading byte offset).  There are no producer warps and no A ring:
-// eight warps copy the next windows with 16-byte cp.async while the tensor core works on the current one, one
-// thread streams the packed weights of a few kernel points at a time through a ring, four warps store finished
-// accumulators.  Taps outside the image are zero texels of the window.
+// by (ky, kx).  A persistent CTA therefore stages, per 16 x 8 pixel tile and per group of 8 or 16 16-byte chunks of
+// input channels, the (16 + Kh - 1) x (8 + Kw - 1) window of the channel-last copy ONCE in shared memory and issues
+// one tcgen05.mma per (kernel point, two chunks) whose A descriptor simply starts (ky * window width + kx) texels
+// further on: the eight pixels of a tile row are eight consecutive texels of a window row (one 8-row group of the
+// K-major operand), the next tile row is one window row further (the descriptor's stride byte offset).  There are
+// no producer warps and no A ring: the next windows are copied while the tensor core works on the current one (by
+// one thread's tensor copies, or in F32X3 mode by eight converting warps, see below), one thread streams the packed
+// weights of a few kernel points at a time through a ring, four warps store finished accumulators.  Taps outside
+// the image are zero texels of the window.
 //
 // With 32 output columns an MMA is a few cycles of tensor work, but a thread issues one only every ~100 cycles,
 // whatever its shape (measured: the same with N = 16 or M = 64, and with independent accumulators).  So kWinAccs
-// threads issue side by side, each the 16-channel slices k ≡ j (mod kWinAccs) of every kernel point into its own
+// warps issue side by side, each the two-chunk slices k ≡ j (mod kWinAccs) of every kernel point into its own
 // accumulator (a partial sum); the epilogue adds the partial sums.  Two such sets sit in tensor memory, so that a
 // tile's stores overlap the next tile's products.
 //
@@ -1238,7 +1237,8 @@ __global__ void __launch_bounds__(CtaShape<NARROW>::kThreads, CtaShape<NARROW>::
 //          rounds them to nearest (the weights are rounded to nearest in both);
 //   F32X3  two windows made by the fill from the float32 copy, hi = bf16(x) and lo = bf16(x - hi), and three
 //          products per slice, hi*Whi into a main accumulator, lo*Whi + hi*Wlo into a cross accumulator: the gather
-//          kernel's arithmetic.
+//          kernel's arithmetic.  Eight warps make them, in the un-swizzled K-major layout [chunk][texel][16 bytes]
+//          (a core matrix = eight consecutive texels of a window row x 16 bytes; leading byte offset = one chunk).
 // In BF16 and TF32 mode nothing touches the texels on their way, so ONE thread brings a window with tensor copies
 // (TMA, cp.async.bulk.tensor; zero fill outside the image comes with it) and the fill warps are not launched.  The
 // window then has the tensor copy's 128-byte-swizzled K-major layout: a texel is one 128-byte row (8 chunks, XOR-ed
