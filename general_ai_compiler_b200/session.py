@@ -151,6 +151,7 @@ class CudaSession:
                                                          dgroups, program.options.get("dcn_math", "f32x3"))
                         self._workspaces[node.id] = (torch.empty(max(need, 16), dtype=torch.uint8, device=self._device)
                                                      if need else None)
+            self._share_input_copies(g, program.options.get("dcn_math", "f32x3"))
             self._pinned_np = {k: t.numpy() for k, t in self._pinned.items()}
         except DeviceUnavailableError:
             raise
@@ -180,6 +181,46 @@ class CudaSession:
         return (weight_name in self._constants and node.id in self._weights_packed
                 and self._workspaces.get(node.id) is not None)
 
+    def _share_input_copies(self, g, math: str) -> None:
+        """Convolutions of the graph that read the same input tensor (the ``conv_offset`` convolution and the DCNv2 it
+        feeds, in every R101-DCN bottleneck) share one channel-last copy of it: their workspaces become views of one
+        buffer that end at the same address, the first of them in graph order makes the copy and the others are told
+        that it is there (``GACB_DCN_INPUT_AT_END`` / ``GACB_DCN_REUSE_INPUT`` of the C ABI)."""
+        torch = self._torch
+        self._input_copy = {}          # node id -> "make" | "reuse"
+        by_input: dict = {}
+        for node in g.nodes:
+            if node.op not in ("Conv2D", "DeformConv2D") or self._workspaces.get(node.id) is None:
+                continue
+            x = g.value_specs[node.inputs[0]]
+            if node.op == "Conv2D":
+                w = g.value_specs[node.inputs[1]]
+                strides, pads, dilations, groups = conv_attrs(node)
+                parts = ops.workspace_parts(*x.shape, w.shape[0], w.shape[2], w.shape[3], strides, pads, dilations, groups, 1,
+                                            math, plain=True)
+            else:
+                w = g.value_specs[node.inputs[3]]
+                stride, padding, dilation, groups, dgroups = dcn_attrs(node)
+                parts = ops.workspace_parts(*x.shape, w.shape[0], w.shape[2], w.shape[3], stride, padding, dilation, groups,
+                                            dgroups, math)
+            if parts[0]:
+                by_input.setdefault((node.inputs[0], parts[0]), []).append((node.id, parts[1]))
+        for (_, copy_bytes), members in by_input.items():
+            if len(members) < 2:
+                continue
+            starts, at = [], 0
+            for _, weight_bytes in members:
+                starts.append(at)
+                at += -(-weight_bytes // 256) * 256
+            buffer = torch.empty(at + copy_bytes, dtype=torch.uint8, device=self._device)
+            for i, ((node_id, _), start) in enumerate(zip(members, starts)):
+                self._workspaces[node_id] = buffer[start:]
+                self._input_copy[node_id] = "make" if i == 0 else "reuse"
+
+    def _input_copy_flags(self, node) -> dict:
+        role = self._input_copy.get(node.id)
+        return {} if role is None else {"input_at_end": True, "reuse_input": role == "reuse"}
+
     def _implementation_for(self, launch: KernelLaunch) -> str:
         return launch.implementation_candidates[0] if launch.implementation_candidates else "unknown"
 
@@ -194,7 +235,7 @@ class CudaSession:
                                dilations=dilations, groups=groups, math=opts.get("dcn_math", "f32x3"), out=out,
                                relu=bool(node.attrs.get("relu", False)), workspace=self._workspaces.get(node.id),
                                status_word=self._status, stream=self._stream,
-                               reuse_weights=self._reuse_weights(node, node.inputs[1]))
+                               reuse_weights=self._reuse_weights(node, node.inputs[1]), **self._input_copy_flags(node))
             self._weights_packed.add(node.id)
             return
         if node.op == FUSED_MSDA:
@@ -230,7 +271,7 @@ class CudaSession:
                               stream=self._stream, mask_is_logits=bool(node.attrs.get("mask_is_logits", False)),
                               relu=bool(node.attrs.get("relu", False)), batch_norm=batch_norm,
                               reuse_weights=self._reuse_weights(node, node.inputs[3]),
-                              test_flags=int(opts.get("dcn_test_flags", 0)))
+                              test_flags=int(opts.get("dcn_test_flags", 0)), **self._input_copy_flags(node))
             self._weights_packed.add(node.id)
             return
         value = args[0]

@@ -242,8 +242,9 @@ size_t gacb_conv2d_workspace_bytes(int n, int Cin, int H, int W, int Cout, int K
 /* Kernel choice for plain convolutions with few output channels.  A whole-image call with groups = 1,
  * stride = dilation = 1, Cout <= 64 (32 in F32X3 mode), Cin a multiple of 64 (32 in TF32 mode) and no BatchNorm
  * runs a persistent kernel that stages each 16 x 8 pixel tile's input window in shared memory once and feeds the
- * tensor core shifted views of it, one per kernel point, instead of gathering every tap (BEVFormer's 27-channel
- * conv_offset: src/gac/models/bevformer/resnet_dcn.py:131-134).  Operands and products are those of the gather
+ * tensor core shifted views of it, one per kernel point, instead of gathering every tap (the 27-channel convolution
+ * that produces DCNv2's offsets and mask scores in an R101-DCN bottleneck; to the reference it is an ordinary
+ * Conv2D, src/gac/core/ops.py:1045-1076).  Operands and products are those of the gather
  * kernel in the same math mode, with two differences: the order of the float32 additions, and in TF32 mode the
  * activations are truncated to tf32 (the tensor core reads the upper 19 bits of the float32 copy) where the gather
  * kernel rounds them to nearest.  The packed weights in the workspace have this kernel's own layout, so

@@ -659,3 +659,39 @@ def test_window_kernel_split_outputs_sharding_and_weight_reuse(dev, window_path)
     strided = ops.conv2d_forward(x, w, b, strides=(2, 2), pads=(1, 1, 1, 1), math="bf16", status_word=status)
     ref = torch.nn.functional.conv2d(x.double(), w.double(), b.double(), stride=2, padding=1)
     assert_rel_gate(strided.cpu().numpy(), ref.float().cpu().numpy(), 1e-2, "strided falls back")
+
+
+def test_session_shares_the_channel_last_copy_between_convolutions_of_one_input(dev):
+    """A graph in which a plain convolution and a DCNv2 read the same X (conv_offset and conv2 of an R101-DCN
+    bottleneck): the session gives them one channel-last copy, made by the first and reused by the second; the
+    results are those of the separate operators, run after run with different X."""
+    from general_ai_compiler_b200 import evaluate_op
+    from general_ai_compiler_b200.bevformer import DcnWorkload, make_workload_inputs
+    from general_ai_compiler_b200.compiler import compile_cuda
+    from general_ai_compiler_b200.ir import Graph, Node, TensorSpec
+    from general_ai_compiler_b200.session import CudaSession
+
+    wl = DcnWorkload("pair", 2, 64, 40, 36, 64, seed=41)
+    x = make_workload_inputs(wl)
+    rng = np.random.default_rng(42)
+    w27 = (rng.standard_normal((27, 64, 3, 3)) * 0.05).astype(np.float32)
+    b27 = rng.standard_normal(27).astype(np.float32)
+    ho, wo = wl.out_hw
+    inputs = {"X": TensorSpec(x["X"].shape, "float32"), "offset": TensorSpec(x["offset"].shape, "float32"),
+              "mask": TensorSpec(x["mask"].shape, "float32")}
+    constants = {"W27": w27, "b27": b27, "W": x["W"], "bias": x["bias"]}
+    nodes = [Node("conv_offset", "Conv2D", ("X", "W27", "b27"), ("T",), {"pads": [1, 1, 1, 1]}),
+             Node("conv2", "DeformConv2D", ("X", "offset", "mask", "W", "bias"), ("Y",), wl.attrs())]
+    graph = Graph("pair_of_convolutions", inputs, ("T", "Y"), nodes, constants)
+    graph.validate()
+    for math, check in (("f32x3", assert_fp32_gate), ("bf16", lambda a, b, what: assert_rel_gate(a, b, 1e-2, what))):
+        with CudaSession(compile_cuda(graph, dcn_math=math)) as session:
+            assert session._input_copy == {"conv_offset": "make", "conv2": "reuse"}
+            assert session._workspaces["conv_offset"].data_ptr() < session._workspaces["conv2"].data_ptr()
+            for run in range(3):                          # the second and third runs reuse the packed weights
+                xr = x["X"] * np.float32(1.0 + 0.25 * run)
+                res = session.run({"X": xr, "offset": x["offset"], "mask": x["mask"]})
+                (t,) = evaluate_op("Conv2D", (xr, w27, b27), {"pads": [1, 1, 1, 1]})
+                (y,) = evaluate_op("DeformConv2D", (xr, x["offset"], x["mask"], x["W"], x["bias"]), wl.attrs())
+                check(res.outputs["T"], t, f"{math} run {run} conv_offset")
+                check(res.outputs["Y"], y, f"{math} run {run} conv2")
