@@ -535,7 +535,7 @@ def bench_other_msda(device, steps: int = 30, warmup: int = 5) -> dict:
                 "ReduceSum, Clamp and Div as separate operators around the first"}
     # the public session API on device-resident inputs: launch by launch against CUDA-graph replay (wall time per
     # invocation of the program's launch sequence; the decoder program is one 8-us kernel, the DCN block three)
-    from general_ai_compiler_b200.bevformer import build_dcn_block_graph, build_msda_graph_for
+    from general_ai_compiler_b200.bevformer import build_dcn_block_graph, build_dcn_bottleneck_graph, build_msda_graph_for
     from general_ai_compiler_b200.compiler import compile_cuda
     from general_ai_compiler_b200.session import CudaSession
 
@@ -548,9 +548,24 @@ def bench_other_msda(device, steps: int = 30, warmup: int = 5) -> dict:
     programs = {"decoder_cross_attention": (build_msda_graph_for(cases["decoder_cross_attention"]),
                                             make_workload_inputs(cases["decoder_cross_attention"])),
                 "dcn_c4_block": (build_dcn_block_graph(WORKLOADS["dcn_c4"]), block_inputs(WORKLOADS["dcn_c4"]))}
+    # the whole deformable stage of a bottleneck as an exporter writes it (conv_offset -> Slice x3 -> Concat ->
+    # Sigmoid -> DeformConv2D -> BatchNorm -> ReLU, weights as graph constants): two launches and one channel-last copy
+    def bottleneck(wl):
+        x = block_inputs(wl)
+        rng = np.random.default_rng(9)
+        k3 = 3 * wl.kernel[0] * wl.kernel[1]
+        constants = {"W_offset": (rng.standard_normal((k3, wl.cin, *wl.kernel)) * (2.0 / (9 * wl.cin)) ** 0.5).astype(np.float32),
+                     "b_offset": np.zeros(k3, np.float32), "W": x["W"], "bias": x["bias"],
+                     **{k: v for k, v in x.items() if k.startswith("bn_")}}
+        return build_dcn_bottleneck_graph(wl, constants, three_way=True), {"X": x["X"]}
+
+    math_of = {}
+    for math in ("f32x3", "tf32", "bf16"):
+        programs[f"dcn_c4_bottleneck/{math}"] = bottleneck(WORKLOADS["dcn_c4"])
+        math_of[f"dcn_c4_bottleneck/{math}"] = math
     replay = {}
     for key, (graph, inputs) in programs.items():
-        program = compile_cuda(graph)
+        program = compile_cuda(graph, dcn_math=math_of.get(key, "f32x3"))
         row = {}
         for label, use_graph in (("launch_by_launch_us", False), ("cuda_graph_us", True)):
             with CudaSession(program, device_id=device.index or 0, check_finite=False, cuda_graph=use_graph) as session:

@@ -306,6 +306,40 @@ def build_tsa_tail_graph(samples: int, queue: int, queries: int, heads: int, hea
     return g
 
 
+def build_dcn_bottleneck_graph(w: DcnWorkload, constants: dict, three_way: bool = False, name: str | None = None) -> Graph:
+    """The deformable 3x3 stage of an R101-DCN bottleneck as a model exporter writes it: a ``conv_offset`` convolution
+    of ``3 * deform_groups * Kh * Kw`` channels over X, its output cut along the channels into offsets and mask
+    scores (``three_way``: mmcv's ``chunk(3)`` with the first two pieces concatenated again), ``Sigmoid`` on the mask
+    scores, ``DeformConv2D`` over the same X, ``BatchNorm``, ``ReLU``.  ``constants`` holds ``W_offset``, ``b_offset``,
+    ``W``, ``bias`` and ``bn_scale`` / ``bn_bias`` / ``bn_mean`` / ``bn_variance``; X is the only input."""
+    kh, kw = w.kernel
+    k = kh * kw * w.deform_groups
+    pads = [w.padding[0], w.padding[1], w.padding[0], w.padding[1]]
+    conv = {"strides": list(w.stride), "pads": pads, "dilations": list(w.dilation)}
+
+    def cut(begin, end):
+        return {"starts": [begin], "ends": [end], "axes": [1], "steps": [1]}
+
+    nodes = [Node("conv_offset", "Conv2D", ("X", "W_offset", "b_offset"), ("offset_mask",), conv)]
+    if three_way:
+        nodes += [Node("chunk_o1", "Slice", ("offset_mask",), ("o1",), cut(0, k)),
+                  Node("chunk_o2", "Slice", ("offset_mask",), ("o2",), cut(k, 2 * k)),
+                  Node("chunk_mask", "Slice", ("offset_mask",), ("mask_scores",), cut(2 * k, 3 * k)),
+                  Node("offset_cat", "Concat", ("o1", "o2"), ("offset",), {"axis": 1})]
+    else:
+        nodes += [Node("take_offset", "Slice", ("offset_mask",), ("offset",), cut(0, 2 * k)),
+                  Node("take_mask", "Slice", ("offset_mask",), ("mask_scores",), cut(2 * k, 3 * k))]
+    nodes += [Node("mask_sigmoid", "Sigmoid", ("mask_scores",), ("mask",)),
+              Node("conv2", "DeformConv2D", ("X", "offset", "mask", "W", "bias"), ("conv2_out",), w.attrs()),
+              Node("bn2", "BatchNorm", ("conv2_out", "bn_scale", "bn_bias", "bn_mean", "bn_variance"), ("normed",),
+                   {"epsilon": 1e-5}),
+              Node("relu2", "ReLU", ("normed",), ("Y",))]
+    g = Graph(name or f"r101_{w.name}_bottleneck", {"X": TensorSpec((w.batch, w.cin, w.height, w.width), "float32", "NCHW")},
+              ("Y",), nodes, dict(constants))
+    g.validate()
+    return g
+
+
 def build_dcn_block_graph(w: DcnWorkload, name: str | None = None) -> Graph:
     """``Sigmoid(mask scores) -> DeformConv2D -> BatchNorm -> ReLU`` as the R101-DCN bottleneck runs them as
     separate dispatches in GAC (175 Sigmoid dispatches in the base profile)."""

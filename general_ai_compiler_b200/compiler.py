@@ -47,6 +47,7 @@ class KernelLaunch:
     block: tuple
     source_nodes: tuple
     implementation_candidates: tuple
+    extra_outputs: tuple = ()      # a Conv2D whose channels go to two tensors: the second one
 
 
 @dataclass
@@ -151,7 +152,7 @@ def _plan(node: Node, specs: dict, options: dict) -> KernelLaunch:
         except Exception as exc:
             _reject(node, str(exc))
         return KernelLaunch(ENTRY_POINTS[node.op], node.id, node.inputs, node.outputs[0], tuple(geo.grid),
-                            tuple(geo.block), node.source_nodes, (geo.kernel.decode(),))
+                            tuple(geo.block), node.source_nodes, (geo.kernel.decode(),), tuple(node.outputs[1:]))
     value, loc = specs[node.inputs[0]], specs[node.inputs[1]]
     b, q, h = loc.shape[0], loc.shape[1], loc.shape[2]
     if len(node.attrs["spatial_shapes"]) > MAX_LEVELS:

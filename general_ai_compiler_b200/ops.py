@@ -295,6 +295,15 @@ def infer_node(node: Node, value_specs: Mapping[str, TensorSpec]) -> dict:
         specs = [value_specs[name] for name in node.inputs]
     except KeyError as exc:
         raise ShapeInferenceError(f"node {node.id!r} uses unknown value {exc.args[0]!r}") from exc
+    if node.op == "Conv2D" and node.attrs.get("split_at") is not None:
+        # produced by passes.fuse_deformable_sampling: the output channels go to two tensors, [0, c) and [c, Cout)
+        whole = _infer_conv(node, specs)
+        cut = node.attrs["split_at"]
+        if len(node.outputs) != 2 or not _is_int(cut) or not isinstance(whole.shape[1], int) or not 0 < int(cut) < whole.shape[1]:
+            raise ShapeInferenceError(f"Conv2D node {node.id!r}: split_at needs two outputs and a cut inside the channels")
+        lo = (whole.shape[0], int(cut), *whole.shape[2:])
+        hi = (whole.shape[0], whole.shape[1] - int(cut), *whole.shape[2:])
+        return {node.outputs[0]: TensorSpec(lo, whole.dtype, whole.layout), node.outputs[1]: TensorSpec(hi, whole.dtype, whole.layout)}
     if len(node.outputs) != 1:
         raise ShapeInferenceError(f"{node.op} node {node.id!r} must have exactly one output")
     if node.op == FUSED_MSDA:

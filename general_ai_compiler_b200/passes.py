@@ -17,7 +17,11 @@ replaces them by one node:
   visibility), min=1))`` behind the output  -> ``reduce="masked_average"``;
 * ``Reshape -> ReduceMean(axis 1)`` behind the output -> ``reduce="mean"``;
 * ``Sigmoid`` in front of the DCNv2 mask, ``BatchNorm`` and ``ReLU`` behind a
-  DCNv2, ``ReLU`` behind a Conv2D.
+  DCNv2, ``ReLU`` behind a Conv2D;
+* ``Slice`` nodes along the channel axis that cut a Conv2D's output in two
+  (the offsets and the mask scores that a ``conv_offset`` convolution makes
+  for the DCNv2 beside it; also the three-way cut whose first two pieces are
+  joined again by a ``Concat``)          -> attr ``split_at``, two outputs.
 
 An intermediate value is only absorbed when nothing else reads it and it is not
 a graph output.  What does not match is left alone; ``Reshape`` nodes that remain
@@ -66,6 +70,15 @@ def infer_neighbour_specs(graph: Graph) -> None:
             out = TensorSpec(tuple(shape), ins[0].dtype)
         elif node.op in ELEMENTWISE_UNARY or node.op == "BatchNorm":
             out = TensorSpec(ins[0].shape, ins[0].dtype)
+        elif node.op == "Slice" and ins[0].is_static:
+            cut = _channel_slice(node, ins[0].shape)
+            if cut is not None:
+                out = TensorSpec((ins[0].shape[0], cut[1] - cut[0], *ins[0].shape[2:]), ins[0].dtype)
+        elif node.op == "Concat" and all(s.is_static for s in ins):
+            axis = int(node.attrs.get("axis", 0)) % ins[0].rank
+            shape = list(ins[0].shape)
+            shape[axis] = sum(s.shape[axis] for s in ins)
+            out = TensorSpec(tuple(shape), ins[0].dtype)
         elif node.op in ELEMENTWISE_BINARY and all(s.is_static for s in ins[:2]):
             out = TensorSpec(tuple(np.broadcast_shapes(ins[0].shape, ins[1].shape)), ins[0].dtype)
         elif node.op in ("ReduceSum", "ReduceMean") and ins[0].is_static:
@@ -78,6 +91,21 @@ def infer_neighbour_specs(graph: Graph) -> None:
             out = TensorSpec(tuple(ins[0].shape[p] for p in perm), ins[0].dtype)
         if out is not None:
             specs[node.outputs[0]] = out
+
+
+def _channel_slice(node: Node, shape) -> Optional[tuple]:
+    """``(begin, end)`` of a Slice that takes a run of whole channels (axis 1, step 1) of a rank-4 tensor and
+    nothing else (the reference's attributes: starts / ends / axes / steps, src/gac/core/ops.py:262-300)."""
+    starts, ends = node.attrs.get("starts"), node.attrs.get("ends")
+    axes, steps = node.attrs.get("axes"), node.attrs.get("steps")
+    if not isinstance(starts, (list, tuple)) or not isinstance(ends, (list, tuple)) or len(starts) != 1 or len(ends) != 1:
+        return None
+    axes = list(axes) if axes is not None else [0]
+    steps = list(steps) if steps is not None else [1]
+    if len(shape) != 4 or len(axes) != 1 or len(steps) != 1 or int(axes[0]) % 4 != 1 or int(steps[0]) != 1:
+        return None
+    begin, end, _ = slice(int(starts[0]), int(ends[0]), 1).indices(int(shape[1]))
+    return (begin, end) if end > begin else None
 
 
 class _Rewriter:
@@ -254,7 +282,14 @@ class _Rewriter:
                 absorbed.append(bn)
                 out_name = bn.outputs[0]
                 what.append("batch norm")
-        if not attrs.get("relu"):
+        outputs = (out_name,)
+        if node.op == "Conv2D" and attrs.get("split_at") is None:
+            split = self.channel_split(out_name)
+            if split is not None:
+                attrs["split_at"], outputs, gone = split
+                absorbed += gone
+                what.append("channel split")
+        if len(outputs) == 1 and not attrs.get("relu"):
             relu = self.only_user(out_name, "ReLU")
             if relu is not None:
                 attrs["relu"] = True
@@ -263,11 +298,40 @@ class _Rewriter:
                 what.append("relu")
         if not what:
             return
-        fused = Node(node.id, node.op, tuple(inputs), (out_name,), attrs,
+        if len(outputs) == 1:
+            outputs = (out_name,)
+        fused = Node(node.id, node.op, tuple(inputs), outputs, attrs,
                      tuple(dict.fromkeys(s for n in [node, *absorbed] for s in n.source_nodes)))
         self.kill(*absorbed)
         self.replaced[node.id] = fused
         self.details.append({"node": node.id, "fused": what, "removed": [n.id for n in absorbed]})
+
+    def channel_split(self, name):
+        """``(cut, (low output, high output), absorbed nodes)`` when the convolution output ``name`` is read only by
+        Slice nodes that cut its channels into [0, cut) and [cut, C) -- two slices, or three whose first two are
+        joined again, in order, by a Concat along the channels that nothing else feeds."""
+        shape = self.shape(name)
+        users = self.uses.get(name, ())
+        if shape is None or len(shape) != 4 or name in self.g.outputs or len(users) not in (2, 3):
+            return None
+        cuts = []
+        for user in users:
+            piece = _channel_slice(user, shape) if user.op == "Slice" and user.id not in self.dead else None
+            if piece is None:
+                return None
+            cuts.append((piece, user))
+        cuts.sort(key=lambda c: c[0])
+        bounds = [c[0] for c in cuts]
+        if bounds[0][0] != 0 or bounds[-1][1] != shape[1] or any(a[1] != b[0] for a, b in zip(bounds, bounds[1:])):
+            return None
+        if len(cuts) == 2:
+            return bounds[0][1], (cuts[0][1].outputs[0], cuts[1][1].outputs[0]), [cuts[0][1], cuts[1][1]]
+        first, second = cuts[0][1].outputs[0], cuts[1][1].outputs[0]
+        join = self.only_user(first, "Concat")
+        if (join is None or self.only_user(second, "Concat") is not join or tuple(join.inputs) != (first, second)
+                or int(join.attrs.get("axis", 0)) % 4 != 1):
+            return None
+        return bounds[1][1], (join.outputs[0], cuts[2][1].outputs[0]), [cuts[0][1], cuts[1][1], join, cuts[2][1]]
 
 
 def _broadcasts(small, full) -> bool:

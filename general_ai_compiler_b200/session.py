@@ -231,8 +231,12 @@ class CudaSession:
         opts = self.program.options
         if node.op == "Conv2D":
             strides, pads, dilations, groups = conv_attrs(node)
+            split = node.attrs.get("split_at")
+            if split is not None:
+                out = (out, self._values[launch.extra_outputs[0]])
             ops.conv2d_forward(args[0], args[1], args[2] if len(args) == 3 else None, strides=strides, pads=pads,
                                dilations=dilations, groups=groups, math=opts.get("dcn_math", "f32x3"), out=out,
+                               split_at=split,
                                relu=bool(node.attrs.get("relu", False)), workspace=self._workspaces.get(node.id),
                                status_word=self._status, stream=self._stream,
                                reuse_weights=self._reuse_weights(node, node.inputs[1]), **self._input_copy_flags(node))

@@ -6,8 +6,8 @@ import numpy as np
 import pytest
 
 from conftest import assert_fp32_gate
-from general_ai_compiler_b200.bevformer import (DcnWorkload, build_dcn_block_graph, build_sca_block_graph,
-                                                build_tsa_tail_graph, make_workload_inputs)
+from general_ai_compiler_b200.bevformer import (DcnWorkload, build_dcn_block_graph, build_dcn_bottleneck_graph,
+                                                build_sca_block_graph, build_tsa_tail_graph, make_workload_inputs)
 from general_ai_compiler_b200.compiler import compile_cuda
 from general_ai_compiler_b200.errors import BackendError
 from general_ai_compiler_b200.ir import Graph, Node, TensorSpec
@@ -150,6 +150,81 @@ def test_fused_tsa_tail_and_dcn_block_match_the_unfused_operators():
                          stride=(1, 1), padding=(1, 1), dilation=(1, 1))
     with CudaSession(compile_cuda(build_dcn_block_graph(wl))) as session:
         assert_fp32_gate(session.run(x).outputs["Y"], want, "fused DCN block")
+
+
+def _bottleneck_constants(wl, seed=3):
+    rng = np.random.default_rng(seed)
+    base = make_workload_inputs(wl)
+    k3 = 3 * wl.kernel[0] * wl.kernel[1]
+    return {"W_offset": (rng.standard_normal((k3, wl.cin, *wl.kernel)) * 0.02).astype(np.float32),
+            "b_offset": (rng.standard_normal(k3) * 0.1).astype(np.float32), "W": base["W"], "bias": base["bias"],
+            "bn_scale": rng.uniform(0.5, 1.5, wl.cout).astype(np.float32), "bn_bias": rng.standard_normal(wl.cout).astype(np.float32),
+            "bn_mean": (rng.standard_normal(wl.cout) * 0.2).astype(np.float32),
+            "bn_variance": rng.uniform(0.3, 2.0, wl.cout).astype(np.float32)}, base["X"]
+
+
+@pytest.mark.parametrize("three_way", [False, True])
+def test_bottleneck_becomes_two_launches(three_way):
+    """conv_offset -> Slice (-> Concat) -> Sigmoid -> DeformConv2D -> BatchNorm -> ReLU: the convolution writes the
+    offsets and the mask scores as two tensors, the DCNv2 takes the sigmoid, the normalisation and the ReLU."""
+    wl = DcnWorkload("neck", 2, 64, 20, 24, 64, seed=5)
+    constants, _ = _bottleneck_constants(wl)
+    g = build_dcn_bottleneck_graph(wl, constants, three_way=three_way)
+    fused, report = fuse_deformable_sampling(g)
+    assert report["changed"] and [n.op for n in fused.nodes] == ["Conv2D", "DeformConv2D"]
+    conv, dcn = fused.nodes
+    assert conv.attrs["split_at"] == 18 and conv.outputs == ("offset", "mask_scores")
+    assert dcn.inputs[:3] == ("X", "offset", "mask_scores") and dcn.attrs["mask_is_logits"] and dcn.attrs["batch_norm"]
+    assert dcn.attrs["relu"] and dcn.outputs == ("Y",)
+    assert fused.value_specs["offset"].shape == (2, 18, 20, 24) and fused.value_specs["mask_scores"].shape == (2, 9, 20, 24)
+    kinds = {d["node"]: d["fused"] for d in report["details"]["fused"]}
+    assert kinds == {"conv_offset": ["channel split"], "conv2": ["sigmoid", "batch norm", "relu"]}
+    program = compile_cuda(g)
+    assert [l.entry_point for l in program.launches] == ["gacb_conv2d_forward", "gacb_dcnv2_fused_forward"] or \
+        [l.entry_point for l in program.launches] == ["gacb_conv2d_forward", "gacb_dcnv2_forward"]
+    assert program.launches[0].output == "offset" and program.launches[0].extra_outputs == ("mask_scores",)
+    # a convolution output that something else reads as well, or that the graph exposes, stays whole
+    nodes = list(g.nodes) + [Node("also_reads", "ReLU", ("offset_mask",), ("side",))]
+    _, report = fuse_deformable_sampling(Graph(g.name, g.inputs, ("Y", "side"), nodes, g.constants))
+    assert all("channel split" not in d["fused"] for d in report["details"]["fused"])
+    exposed = Graph(g.name, g.inputs, ("Y", "offset_mask"), g.nodes, g.constants)
+    _, report = fuse_deformable_sampling(exposed)
+    assert all("channel split" not in d["fused"] for d in report["details"]["fused"])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("math", ["f32x3", "bf16"])
+def test_bottleneck_session_matches_the_operator_chain(math):
+    """The session's two launches against the same two operators called by hand (bit-identical: same kernels), and
+    against the C oracle's chain at the gate the chain test uses (an offset that differs in the last bit moves a
+    sample across a texel)."""
+    import torch
+
+    from general_ai_compiler_b200 import ops
+    from general_ai_compiler_b200.session import CudaSession
+    from oracle import conv2d_c, dcnv2_fused_c
+
+    wl = DcnWorkload("neck", 2, 64, 40, 36, 64, seed=6)
+    constants, x = _bottleneck_constants(wl, seed=4)
+    g = build_dcn_bottleneck_graph(wl, constants, three_way=True)
+    with CudaSession(compile_cuda(g, dcn_math=math)) as session:
+        assert session._input_copy == {"conv_offset": "make", "conv2": "reuse"}
+        first = session.run({"X": x}).outputs["Y"]
+        again = session.run({"X": x}).outputs["Y"]            # packed weights reused
+    assert np.array_equal(first, again)
+    device = ops.require_device(0)
+    t = {k: torch.from_numpy(v).to(device) for k, v in {**constants, "X": x}.items()}
+    off, scores = ops.conv2d_forward(t["X"], t["W_offset"], t["b_offset"], pads=(1, 1, 1, 1), math=math, split_at=18)
+    y = ops.dcnv2_forward(t["X"], off, scores, t["W"], t["bias"], stride=wl.stride, padding=wl.padding, dilation=wl.dilation,
+                          math=math, mask_is_logits=True, relu=True,
+                          batch_norm=(t["bn_scale"], t["bn_bias"], t["bn_mean"], t["bn_variance"], 1e-5))
+    assert np.array_equal(first, y.cpu().numpy())
+    om = conv2d_c(x, constants["W_offset"], constants["b_offset"], pads=(1, 1, 1, 1))
+    want = dcnv2_fused_c(x, np.ascontiguousarray(om[:, :18]), np.ascontiguousarray(om[:, 18:]), constants["W"], constants["bias"],
+                         bn=(constants["bn_scale"], constants["bn_bias"], constants["bn_mean"], constants["bn_variance"], 1e-5),
+                         relu=True, stride=wl.stride, padding=wl.padding, dilation=wl.dilation)
+    scale = float(np.abs(want).max())
+    assert float(np.abs(first - want).max()) <= (1e-3 if math == "f32x3" else 2e-2) * scale
 
 
 @pytest.mark.gpu
