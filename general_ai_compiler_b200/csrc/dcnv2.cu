@@ -1750,22 +1750,9 @@ int launch_conv_window(const DcnArgs &a, ConvWinArgs &u, size_t smem, const void
   CUtensorMap xt_map{};
   if (WinTraits<MODE>::kTma) {
     // X_t as a 4-D tensor (channels, width, height, image), innermost first; a box is one window of one channel group
-    using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-    static std::atomic<EncodeFn> encode{nullptr};
-    EncodeFn fn = encode.load();
-    if (!fn) {
-      void *sym = nullptr;
-      cudaDriverEntryPointQueryResult found;
-      const int rc = check_cuda(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &found),
-                                "cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)");
-      if (rc != GACB_OK) return rc;
-      if (found != cudaDriverEntryPointSuccess || !sym)
-        return fail(GACB_ERR_UNSUPPORTED, "conv2d: the driver does not provide cuTensorMapEncodeTiled");
-      fn = reinterpret_cast<EncodeFn>(sym);
-      encode.store(fn);
-    }
+    TensorMapEncoder fn = nullptr;
+    const int rc = tensor_map_encoder(&fn);
+    if (rc != GACB_OK) return rc;
     const cuuint64_t es = WinTraits<MODE>::kTf32 ? 4 : 2;
     const cuuint64_t dims[4] = {(cuuint64_t)a.Cin, (cuuint64_t)a.W, (cuuint64_t)a.H, (cuuint64_t)(a.n_end - a.n_begin)};
     const cuuint64_t strides[3] = {(cuuint64_t)a.Cin * es, (cuuint64_t)a.W * a.Cin * es, (cuuint64_t)a.H * a.W * a.Cin * es};

@@ -1,9 +1,31 @@
 // Library-wide entry points: version, error text, device queries.
 #include <stdarg.h>
 
+#include <cuda.h>   // CUtensorMap types for tensor_map_encoder (declared in the common header when this comes first)
+
+#include <atomic>
+
 #include "gacb_common.cuh"
 
 namespace gacb {
+
+int tensor_map_encoder(TensorMapEncoder *fn) {
+  static std::atomic<TensorMapEncoder> cached{nullptr};
+  TensorMapEncoder f = cached.load();
+  if (!f) {
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult found;
+    const int rc = check_cuda(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &found),
+                              "cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)");
+    if (rc != GACB_OK) return rc;
+    if (found != cudaDriverEntryPointSuccess || !sym)
+      return fail(GACB_ERR_UNSUPPORTED, "the driver does not provide cuTensorMapEncodeTiled");
+    f = reinterpret_cast<TensorMapEncoder>(sym);
+    cached.store(f);
+  }
+  *fn = f;
+  return GACB_OK;
+}
 
 static thread_local char g_error[512] = "";
 

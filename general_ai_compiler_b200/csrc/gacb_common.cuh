@@ -72,6 +72,15 @@ __device__ __forceinline__ long long checked_index(long long index, long long li
 int msda_check_record(unsigned int out[2]);
 int dcn_check_record(unsigned int out[2]);
 
+// cuTensorMapEncodeTiled of the driver, looked up once through the runtime (the library does not link libcuda).
+// Declared with plain pointer types so that this header does not need <cuda.h>; cast the arguments at the call.
+#ifdef CUDA_VERSION
+using TensorMapEncoder = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                      const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                      CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+int tensor_map_encoder(TensorMapEncoder *fn);
+#endif
+
 // mbarrier and bulk-copy wrappers (sm_90+ PTX) shared by the kernels that stage tiles in shared memory.
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
