@@ -88,6 +88,11 @@ def test_conv2d_random_shapes(seed, dev, checked):
     random_tests.test_conv2d_random_shapes(seed, dev)
 
 
+@pytest.mark.parametrize("seed", range(0, 12, 4))
+def test_window_convolution_random_shapes(seed, dev, checked):
+    random_tests.test_window_convolution_random_shapes(seed, dev)
+
+
 @pytest.mark.parametrize("label,wl_args", [
     ("two_deformable_groups", dict(cin=128, cout=64, deform_groups=2)),
     ("groups_and_deformable_groups", dict(cin=256, cout=128, groups=2, deform_groups=4)),

@@ -178,3 +178,56 @@ def test_conv2d_random_shapes(seed, dev):
                                     groups=groups, relu=relu, split_at=cut, status_word=status)
         torch.cuda.synchronize()
         assert torch.equal(lo, got[:, :cut]) and torch.equal(hi, got[:, cut:])
+
+
+def _round_like_the_mode(x, w, math):
+    """Operands as the tensor core sees them in each mode of the window kernel: bf16-rounded (BF16), activations
+    truncated and weights rounded to tf32 (TF32), unchanged (F32X3: the float32 product)."""
+    import torch
+
+    if math == "bf16":
+        r = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(torch.bfloat16).float().numpy()
+        return r(x), r(w)
+    if math == "tf32":
+        xb = np.ascontiguousarray(x, np.float32).view(np.uint32) & np.uint32(0xFFFFE000)
+        wb = (np.ascontiguousarray(w, np.float32).view(np.uint32) + np.uint32(0x1000)) & np.uint32(0xFFFFE000)
+        return xb.view(np.float32), wb.view(np.float32)
+    return x, w
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_window_convolution_random_shapes(seed, dev):
+    """Shapes that take the persistent window kernel (whole images, stride 1, no dilation, no groups, at most 64
+    output channels, channels a multiple of 64): ragged tiles, every kernel extent, uneven pads, one to three
+    images, all three math modes, each at the float32 gate against the oracle on that mode's operands."""
+    from oracle import conv2d_c
+
+    torch, ops, device = dev
+    rng = np.random.default_rng(7000 + seed)
+    n = int(rng.integers(1, 4))
+    cin = int(rng.choice([64, 128, 192, 256]))
+    cout = int(rng.choice([1, 5, 16, 27, 32, 33, 64]))
+    kh, kw = int(rng.choice([1, 3, 5])), int(rng.choice([1, 3, 5]))
+    h, w = int(rng.integers(17, 50)), int(rng.integers(9, 60))
+    pads = tuple(int(v) for v in rng.integers(0, 3, 4))
+    relu = bool(seed % 2)
+    x = rng.standard_normal((n, cin, h, w)).astype(np.float32)
+    wt = (rng.standard_normal((cout, cin, kh, kw)) * np.sqrt(2.0 / (kh * kw * cin))).astype(np.float32)
+    bias = rng.standard_normal(cout).astype(np.float32) if seed % 3 else None
+    xd, wd = torch.from_numpy(x).to(device), torch.from_numpy(wt).to(device)
+    bd = torch.from_numpy(bias).to(device) if bias is not None else None
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    for math in ("f32x3", "tf32", "bf16"):
+        xr, wr = _round_like_the_mode(x, wt, math)
+        want = conv2d_c(xr, wr, bias, pads=pads, relu=relu)
+        geo = ops.native.dcnv2_launch_geometry(n, cin, h, w, cout, kh, kw, (1, 1), pads[:2], (1, 1), 1, 1,
+                                               ops.native.DCN_MATH_MODES[math], plain=True)
+        got = ops.conv2d_forward(xd, wd, bd, pads=pads, math=math, relu=relu, status_word=status)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        if geo.kernel.startswith(b"conv_window_kernel") and pads[0] == pads[2] and pads[1] == pads[3]:
+            assert_fp32_gate(got.cpu().numpy(), want, f"window conv seed {seed} {math}")
+        elif math == "f32x3":
+            assert_fp32_gate(got.cpu().numpy(), want, f"conv seed {seed} {math}")
+        else:      # another kernel took it (small problems stay on the CUDA cores in float32; F32X3 beyond 32 channels)
+            assert_rel_gate(got.cpu().numpy(), conv2d_c(x, wt, bias, pads=pads, relu=relu), 1e-2, f"conv seed {seed} {math}")
