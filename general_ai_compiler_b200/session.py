@@ -31,7 +31,7 @@ from .compiler import TARGET, VIEW_OPS, CudaProgram, KernelLaunch
 from .errors import BackendError, DeviceUnavailableError, ValidationError
 from .ops import FUSED_MSDA, conv_attrs, dcn_attrs
 from .profiler import Profiler
-from .validation import bind_inputs, parallel_copy
+from .validation import all_finite, bind_inputs, checked_copy, parallel_copy
 
 
 @dataclass
@@ -180,6 +180,21 @@ class CudaSession:
         """Weights that are graph constants never change between runs: pack them on the first launch only."""
         return (weight_name in self._constants and node.id in self._weights_packed
                 and self._workspaces.get(node.id) is not None)
+
+    def _stage_and_upload(self, name: str, arr: np.ndarray) -> None:
+        """Host array -> pinned staging buffer (checked for non-finite values on the way when the session checks: one
+        pass over the input instead of a check and a copy) -> device; the host->device copy of one input runs while
+        the next one is staged.  (Staging and uploading slab by slab along the first axis was measured slower:
+        41 ms against 24 ms per run of the base spatial workload.)"""
+        staged = self._pinned_np[name]
+        if arr.ctypes.data == staged.ctypes.data:                   # the caller filled the pinned view itself
+            if self._check_finite and not all_finite(arr):
+                raise ValidationError(f"input {name!r} must contain finite values")
+        elif self._check_finite:
+            checked_copy(staged, arr, name)
+        else:
+            parallel_copy(staged, arr)
+        self._inputs[name].copy_(self._pinned[name], non_blocking=True)
 
     def _share_input_copies(self, g, math: str) -> None:
         """Convolutions of the graph that read the same input tensor (the ``conv_offset`` convolution and the DCNv2 it
@@ -389,12 +404,15 @@ class CudaSession:
             if self._closed or self._failed:
                 raise BackendError("CUDA Session is closed or failed; create a new Session")
             started = time.perf_counter()
-            bound = bind_inputs(self.program.graph, inputs, check_finite=self._check_finite)
             torch = self._torch
             instrument = trace or profile
+            overlapped = not instrument and self._can_overlap()
+            # Names, shapes, dtypes and contiguity first.  The finite check of the general path rides on the staging
+            # copy below (one pass over the inputs instead of two); no kernel is launched before every input passed.
+            bound = bind_inputs(self.program.graph, inputs, check_finite=self._check_finite and overlapped)
             profiler = Profiler(enabled=instrument)
             event_pairs: list = []
-            if not instrument and self._can_overlap():
+            if overlapped:
                 with torch.cuda.device(self._device):
                     gpu_ms = self._run_overlapped(bound)
                     outputs = {name: (self._fresh_copy(self._pinned_out[name].numpy()) if self._fresh_outputs
@@ -407,10 +425,7 @@ class CudaSession:
                 nbytes = sum(v.nbytes for v in bound.values())
                 with profiler.record("copy_h2d", "inputs", TARGET, metadata={"bytes": nbytes, "clock": "host submission"}):
                     for name, arr in bound.items():
-                        staged = self._pinned_np[name]
-                        if arr.ctypes.data != staged.ctypes.data:   # caller did not fill the pinned view in place
-                            parallel_copy(staged, arr)
-                        self._inputs[name].copy_(self._pinned[name], non_blocking=True)
+                        self._stage_and_upload(name, arr)
                 self._launch_all(profiler, instrument, event_pairs)
                 end.record(self._stream)
                 with profiler.record("copy_d2h", "outputs", TARGET, metadata={"clock": "host including completion wait"}):

@@ -37,8 +37,11 @@ def host_pool():
 
 
 def _pieces(arr: np.ndarray):
+    """Flat views of at most ``_CHUNK_BYTES``, and at least two per pool thread when the array is large enough for
+    that (pieces of 1 MB or more), so that a 30 MB slab keeps the whole pool busy as well."""
     flat = arr.reshape(-1)
-    step = max(1, _CHUNK_BYTES // max(1, arr.itemsize))
+    nbytes = min(_CHUNK_BYTES, max(1 << 20, arr.nbytes // 32))
+    step = max(1, nbytes // max(1, arr.itemsize))
     return [flat[i:i + step] for i in range(0, flat.size, step)]
 
 
@@ -55,6 +58,36 @@ def parallel_copy(dst: np.ndarray, src: np.ndarray) -> None:
         np.copyto(dst, src)
         return
     list(host_pool().map(lambda pair: np.copyto(pair[0], pair[1]), zip(_pieces(dst), _pieces(src))))
+
+
+_CACHE_BYTES = 512 << 10   # a piece this small is still in the core's cache when it is read a second time
+
+
+def checked_copy(dst: np.ndarray, src: np.ndarray, name: str) -> None:
+    """``np.copyto(dst, src)`` that also raises ``ValidationError`` when ``src`` holds a non-finite value, as ONE pass
+    over memory: every piece is tested and then copied while it is still in cache, pieces spread over the host pool
+    (a separate ``all_finite`` and ``parallel_copy`` read the source from memory twice).  ``dst`` is written up to
+    the piece that failed."""
+    if not (dst.flags.c_contiguous and src.flags.c_contiguous) or dst.shape != src.shape:
+        if not all_finite(src):
+            raise ValidationError(f"input {name!r} must contain finite values")
+        np.copyto(dst, src)
+        return
+    step = max(1, _CACHE_BYTES // max(1, src.itemsize))
+
+    def one(pair) -> bool:
+        d, s = pair
+        ok = True
+        for i in range(0, s.size, step):
+            piece = s[i:i + step]
+            ok = ok and bool(np.isfinite(piece).all())
+            d[i:i + step] = piece
+        return ok
+
+    pairs = list(zip(_pieces(dst), _pieces(src)))
+    results = map(one, pairs) if src.nbytes <= 2 * _CHUNK_BYTES else host_pool().map(one, pairs)
+    if not all(list(results)):
+        raise ValidationError(f"input {name!r} must contain finite values")
 
 
 def bind_inputs(graph: Graph, inputs: Mapping[str, np.ndarray], *, check_finite: bool = True) -> dict:

@@ -476,3 +476,33 @@ def test_tile_kernel_samples_far_from_their_cell_and_softmax_form(dev):
             assert_fp32_gate(soft.cpu().numpy(), msda_logits_forward(value, loc, logits, shapes), f"tile softmax {hh}x{ww}")
         finally:
             _tile_mode(previous)
+
+
+def test_session_rejects_non_finite_inputs_on_the_staging_pass_and_stays_usable(dev):
+    """The default session checks for non-finite values while it copies the inputs into its pinned buffers, slab by
+    slab, before any kernel is launched: a NaN in the last camera raises ``ValidationError``, and the next run with
+    clean inputs gives the oracle's result."""
+    from general_ai_compiler_b200.bevformer import WORKLOADS, build_msda_graph_for, make_workload_inputs
+    from general_ai_compiler_b200.compiler import compile_cuda
+    from general_ai_compiler_b200.errors import ValidationError
+    from general_ai_compiler_b200.session import CudaSession
+    from oracle import msda_c
+
+    w = WORKLOADS["base_sca"].with_queries(300)          # value is large enough to be staged camera by camera
+    x = make_workload_inputs(w)
+    want = msda_c(x["value"], x["sampling_locations"], x["attention_weights"], w.spatial_shapes)
+    with CudaSession(compile_cuda(build_msda_graph_for(w))) as session:
+        assert_fp32_gate(session.run(x).outputs["output"], want, "default session")
+        for name in ("value", "sampling_locations", "attention_weights"):
+            bad = {k: v.copy() for k, v in x.items()}
+            bad[name].reshape(-1)[-3] = np.inf
+            with pytest.raises(ValidationError, match=f"input '{name}' must contain finite values"):
+                session.run(bad)
+        assert_fp32_gate(session.run(x).outputs["output"], want, "after rejected inputs")
+        pinned = session.pinned_inputs()                  # filled in place: checked where they are
+        for k, v in x.items():
+            np.copyto(pinned[k], v)
+        assert_fp32_gate(session.run(pinned).outputs["output"], want, "pinned inputs")
+        pinned["value"].reshape(-1)[5] = np.nan
+        with pytest.raises(ValidationError, match="finite"):
+            session.run(pinned)

@@ -261,6 +261,26 @@ def test_bind_inputs_enforces_the_graph_abi():
         bind_inputs(g, dict(x, value=bad))
 
 
+def test_checked_copy_copies_and_finds_non_finite_values_in_one_pass():
+    from general_ai_compiler_b200.validation import checked_copy
+
+    rng = np.random.default_rng(3)
+    for shape in ((7,), (3, 1000, 33), (6, 1 << 20)):          # below and above the pooled size
+        src = rng.standard_normal(shape).astype(np.float32)
+        dst = np.full(shape, 7.0, np.float32)
+        checked_copy(dst, src, "x")
+        assert np.array_equal(dst, src)
+        for bad in (np.nan, np.inf, -np.inf):
+            poisoned = src.copy()
+            poisoned.reshape(-1)[poisoned.size - 2] = bad
+            with pytest.raises(ValidationError, match="input 'x' must contain finite values"):
+                checked_copy(dst, poisoned, "x")
+    # a destination that is not contiguous still gets the values
+    wide = np.zeros((4, 10), np.float32)
+    checked_copy(wide[:, ::2], np.ones((4, 5), np.float32), "y")
+    assert wide[:, ::2].sum() == 20 and wide[:, 1::2].sum() == 0
+
+
 def test_compare_tensor_metrics():
     ref = np.linspace(-1, 1, 101, dtype=np.float32)
     same = compare_tensor(ref, ref)
