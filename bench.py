@@ -63,7 +63,7 @@ UNIT = "Gsamples/s"
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of msda_rows_kernel on the base_sca workload: constants
 # taken from one ncu capture of a full-size launch, not measured by this run (ncu cannot run inside a timed bench).
-NCU_TRAFFIC_BYTES = {"float32": 467_982_336, "bfloat16": 463_020_032}
+NCU_TRAFFIC_BYTES = {"float32": 467_982_336, "bfloat16": 350_548_736}
 NCU_TRAFFIC_SOURCE = "constant from an ncu capture (one full-size launch, 2026-11-25), not measured in this run"
 
 

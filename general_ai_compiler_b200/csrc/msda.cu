@@ -60,6 +60,9 @@ constexpr int kMaxCoordRank = 8;
 #ifndef GACB_MSDA_RECORDS_PER_THREAD
 #define GACB_MSDA_RECORDS_PER_THREAD 2
 #endif
+#ifndef GACB_MSDA_RECORDS_PER_THREAD_BF16
+#define GACB_MSDA_RECORDS_PER_THREAD_BF16 4
+#endif
 #ifndef GACB_MSDA_CARVEOUT
 #define GACB_MSDA_CARVEOUT 60
 #endif
@@ -69,7 +72,15 @@ constexpr int kMaxCoordRank = 8;
 #ifndef GACB_MSDA_UNROLL
 #define GACB_MSDA_UNROLL 4
 #endif
-constexpr int kRecordsPerThread = GACB_MSDA_RECORDS_PER_THREAD;   // phase-A budget: 20-byte tap records per thread of the CTA
+constexpr int kRecordsPerThread = GACB_MSDA_RECORDS_PER_THREAD;
+// Phase-A budget (kRecordsPerThread; RowsCta<VT>::kRecordsPerThreadLongRows for rows longer than that table): 20-byte
+// tap records per thread of the CTA.  It sets how many
+// samples of a row a CTA takes at a time, and with that the size of the pieces in which it streams the row's
+// locations and weights.  Pieces shorter than a 128-byte line cost extra DRAM reads (measured with the spatial
+// workload: the rest of the line is read from DRAM again when the next chunk asks for it).  fp32 texels, 2 records per
+// thread (64-byte pieces of the weights): 416 MB read, 408 us; 4 per thread (whole rows): 374 MB = every input
+// once, but 419 us -- the kernel is not DRAM-bound, so it keeps 2.  bf16 texels, 2 per thread (64- and 32-byte
+// pieces): 425 MB, 345 us; 4 per thread: 312 MB, 335 us.
 constexpr int kMaxRowsPerGroup = 8;
 constexpr int kCarveoutPercent = GACB_MSDA_CARVEOUT;  // shared-memory share of the 256 KB; the rest is L1
 constexpr int kUnroll = GACB_MSDA_UNROLL;            // samples whose 4*kUnroll tap loads are in flight together
@@ -349,10 +360,12 @@ struct RowsCta;
 template <>
 struct RowsCta<float> {
   static constexpr int kThreads = GACB_MSDA_THREADS_F32;
+  static constexpr int kRecordsPerThreadLongRows = GACB_MSDA_RECORDS_PER_THREAD;
 };
 template <>
 struct RowsCta<__nv_bfloat16> {
   static constexpr int kThreads = GACB_MSDA_THREADS_BF16;
+  static constexpr int kRecordsPerThreadLongRows = GACB_MSDA_RECORDS_PER_THREAD_BF16;
 };
 
 // LPR lanes per row, CPL channels per lane (D == LPR*CPL).
@@ -863,8 +876,10 @@ template <typename VT, int LPR>
 RowsGeometry plan_rows(MsdaArgs &a) {
   constexpr int kThreads = RowsCta<VT>::kThreads;
   constexpr int RPI = kThreads / LPR;
-  constexpr int kEntriesPerCta = kThreads * kRecordsPerThread;
-  const int cap = kEntriesPerCta / RPI > kUnroll ? kEntriesPerCta / RPI : kUnroll;
+  // rows that do not fit the small table are taken in chunks; those chunks may use the larger table of this texel type
+  const int small_cap = kThreads * kRecordsPerThread / RPI;
+  const int entries = a.LP <= small_cap ? kThreads * kRecordsPerThread : kThreads * RowsCta<VT>::kRecordsPerThreadLongRows;
+  const int cap = entries / RPI > kUnroll ? entries / RPI : kUnroll;
   if (a.LP <= cap) {
     a.chunk_len = a.LP;
     a.chunk_pad = (a.LP + kUnroll - 1) / kUnroll * kUnroll;
